@@ -358,6 +358,78 @@ typedef struct b200_linear_int8_args {
 size_t b200_linear_int8_workspace_bytes(int64_t M, int64_t K);
 int b200_linear_int8(const b200_linear_int8_args* args, b200_stream_t stream);
 
+
+/* ---- models with an fp32 residual stream, latent attention and sparse experts --------------------------------
+ * (no counterpart in the reference, whose models keep the residual in the compute dtype, cache full keys and values and
+ * whose only expert layer is the dense-routed LLaMAMoE of lit_gpt/model.py).  `dtype` is the matrix-product dtype of
+ * weights and activations, B200_BF16 or B200_F32; statistics, softmax, router and the residual are fp32 in both. */
+/* x[row] = embed[tokens[row]] * scale + pos_table[pos[row]] (fp32), act[row] = dtype(x[row]); pos_table may be NULL */
+int b200_embed_pos(const int32_t* tokens, const int32_t* pos, const void* embed, const void* pos_table, float scale, float* x,
+                   void* act, int64_t rows, int d, int vocab, int max_pos, int dtype, b200_stream_t stream);
+/* out[out_rows[i]] = in[in_rows[i]] / sqrt(mean(in^2) + eps) * (weight, or 1 + weight when plus_one); NULL index arrays
+ * mean i itself, an out row < 0 is skipped.  One or two segments per launch (e.g. the two halves of a fused projection,
+ * the second scattered straight into a cache). */
+typedef struct b200_rms_rows_seg {
+  const void* in;
+  const void* weight;
+  void* out;
+  const int64_t* in_rows;
+  const int64_t* out_rows;
+  int64_t ld_in, ld_out;
+  int d, plus_one;
+} b200_rms_rows_seg;
+int b200_rms_rows(const b200_rms_rows_seg* segs, int n_segs, int64_t rows, float eps, int in_dtype, int out_dtype, b200_stream_t stream);
+/* x[row] += y[row] / sqrt(mean(y[row]^2) + eps) * (1 + weight); act[row] = dtype(x[row]) */
+int b200_residual_norm_add(const void* y, const void* weight, float eps, float* x, void* act, int64_t rows, int d, int dtype,
+                           b200_stream_t stream);
+int b200_gather_rows(const void* src, const int64_t* rows, void* dst, int64_t n_rows, int d, int dtype, b200_stream_t stream);
+int b200_scale_f32(const void* in, float scale, float* out, int64_t n, int dtype, b200_stream_t stream);
+
+/* Ragged causal attention with separate query-key (dk) and value (dv) sizes and no rotation.  seqs[s] = {first query row,
+ * query rows, position of the first query row, row of position 0 in k / v}; query row i of sequence s sees key rows
+ * kv0 .. kv0 + pos0 + i.  q (rows, n_head * dk), k (.., n_head * dk), v (.., n_head * dv), out (rows, n_head * dv), each
+ * with its own leading dimension. */
+typedef struct b200_latent_prefill_args {
+  const void* q; const void* k; const void* v; void* out;
+  int64_t ldq, ldk, ldv, ldo;
+  const int32_t* seqs;   /* int32[n_seqs][4], 16-byte aligned */
+  int n_seqs, max_q_len, n_head, dk, dv;
+  float scale;
+  int dtype;
+} b200_latent_prefill_args;
+int b200_latent_prefill(const b200_latent_prefill_args* args, b200_stream_t stream);
+/* One query row per sequence over cached latents (slots, max_seq, r): sequence b reads positions 0 .. row_pos[b] of slot
+ * row_slot[b] (its own latent already stored).  w_uk (n_head * dk, r) and w_uv (n_head * dv, r) are absorbed: no keys or
+ * values are materialised.  n_split CTAs share each (sequence, head); the workspace holds their partial results. */
+typedef struct b200_latent_decode_args {
+  const void* q; const void* w_uk; const void* w_uv; const void* cache; void* out;
+  int64_t ldq, ldo, slot_stride;
+  const int32_t* row_slot; const int32_t* row_pos;
+  int batch, n_head, dk, dv, r, max_seq, n_split;
+  float scale;
+  int dtype;
+  void* workspace; size_t workspace_bytes;
+} b200_latent_decode_args;
+size_t b200_latent_decode_workspace_bytes(int batch, int n_head, int r, int n_split);
+int b200_latent_decode(const b200_latent_decode_args* args, b200_stream_t stream);
+
+/* Router: s = sigmoid(W_router x); experts are chosen by s + correction among the `keep` best of `n_group` equal groups of
+ * neighbours (group rank = sum of its two largest corrected scores); weights[t, k] = s of the chosen expert. */
+int b200_moe_route(const void* x, const void* w_router, const void* correction, int32_t* ids, float* weights, int64_t tokens, int d,
+                   int n_expert, int top, int n_group, int keep, int dtype, b200_stream_t stream);
+/* counting sort of the (token, choice) pairs by expert: expert_off[E + 1], tile_off[E + 1] (64-row tiles), slot_token[tokens * top],
+ * slot_of[tokens * top] */
+int b200_moe_plan(const int32_t* ids, int64_t tokens, int top, int n_expert, int32_t* expert_off, int32_t* tile_off, int32_t* slot_token,
+                  int32_t* slot_of, b200_stream_t stream);
+/* c[row, :n] = act(a[row_src ? row_src[row] : row, :k] . w[e][:n, :k]^T) for the rows of every expert e; act = relu^2 or none */
+int b200_moe_gemm(const void* a, int64_t lda, const int32_t* row_src, const void* w, void* c, int64_t ldc, const int32_t* expert_off,
+                  const int32_t* tile_off, int64_t rows, int n_expert, int n, int k, int sqrelu, int dtype, b200_stream_t stream);
+/* few tokens: hidden = relu(W_up[e] x)^2 per (token, choice), out[t] = sum_k weights[t, k] * W_down[e_k] hidden[t, k] */
+int b200_moe_gemv(const void* x, const int32_t* ids, const float* weights, const void* w_up, const void* w_down, void* hidden, void* out,
+                  int64_t tokens, int top, int d, int ff, int dtype, b200_stream_t stream);
+int b200_moe_combine(const void* y, const int32_t* slot_of, const float* weights, void* out, int64_t tokens, int top, int d, int dtype,
+                     b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

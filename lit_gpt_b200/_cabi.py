@@ -74,6 +74,47 @@ class QGemmArgs(ctypes.Structure):
     ]
 
 
+class RmsRowsSeg(ctypes.Structure):  # mirrors b200_rms_rows_seg
+    _fields_ = [("inp", c_void_p), ("weight", c_void_p), ("out", c_void_p), ("in_rows", c_void_p), ("out_rows", c_void_p),
+                ("ld_in", c_int64), ("ld_out", c_int64), ("d", c_int), ("plus_one", c_int)]
+
+
+class LatentPrefillArgs(ctypes.Structure):  # mirrors b200_latent_prefill_args
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p),
+                ("ldq", c_int64), ("ldk", c_int64), ("ldv", c_int64), ("ldo", c_int64), ("seqs", c_void_p),
+                ("n_seqs", c_int), ("max_q_len", c_int), ("n_head", c_int), ("dk", c_int), ("dv", c_int),
+                ("scale", c_float), ("dtype", c_int)]
+
+
+class LatentDecodeArgs(ctypes.Structure):  # mirrors b200_latent_decode_args
+    _fields_ = [("q", c_void_p), ("w_uk", c_void_p), ("w_uv", c_void_p), ("cache", c_void_p), ("out", c_void_p),
+                ("ldq", c_int64), ("ldo", c_int64), ("slot_stride", c_int64), ("row_slot", c_void_p), ("row_pos", c_void_p),
+                ("batch", c_int), ("n_head", c_int), ("dk", c_int), ("dv", c_int), ("r", c_int), ("max_seq", c_int), ("n_split", c_int),
+                ("scale", c_float), ("dtype", c_int), ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
+
+
+# Entry points of the sources every model needs (library state, norms, sampling) and of the fp32-residual / latent-attention /
+# expert kernels: `load_core()` can serve them from a library built from those sources alone.
+_CORE_SOURCES = ("api.cu", "norm.cu", "sample.cu", "resid.cu", "latent.cu", "moe.cu")
+_CORE_SIGNATURES = {
+    "b200_embed_pos": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_rms_rows": (c_int, [ctypes.POINTER(RmsRowsSeg), c_int, c_int64, c_float, c_int, c_int, c_void_p]),
+    "b200_residual_norm_add": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "b200_scale_f32": (c_int, [c_void_p, c_float, c_void_p, c_int64, c_int, c_void_p]),
+    "b200_latent_prefill": (c_int, [ctypes.POINTER(LatentPrefillArgs), c_void_p]),
+    "b200_latent_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "b200_latent_decode": (c_int, [ctypes.POINTER(LatentDecodeArgs), c_void_p]),
+    "b200_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_moe_plan": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200_moe_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                              c_void_p]),
+    "b200_moe_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+}
+_CORE_SHARED = ("b200_abi_version", "b200_last_error", "b200_device_info", "b200_set_pdl", "b200_launch_count", "b200_rmsnorm", "b200_swiglu",
+                "b200_embedding", "b200_argmax", "b200_sample")
+
 _SIGNATURES = {
     "b200_abi_version": (c_int, []),
     "b200_last_error": (c_char_p, []),
@@ -126,7 +167,11 @@ _SIGNATURES = {
     "b200_qgemm_tune": (c_int, [c_int]),
 }
 
+_SIGNATURES.update(_CORE_SIGNATURES)
+
 _lib = None
+_core = None
+CORE_LIB_PATH = os.path.join(_PKG, "lib", "libb200gpt_core.so")
 
 
 class B200Error(RuntimeError):
@@ -155,13 +200,41 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     return lib
 
 
+def _bind(lib: ctypes.CDLL, names) -> ctypes.CDLL:
+    for name in names:
+        res, args = _SIGNATURES[name]
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    if lib.b200_abi_version() != 1:
+        raise B200Error(f"libb200gpt ABI version {lib.b200_abi_version()} != 1")
+    return lib
+
+
+def load_core() -> ctypes.CDLL:
+    """The library for models that need none of the quantized-weight kernels: the full library when it is already loaded or
+    built and current, else ``libb200gpt_core.so``, built in-tree from ``_CORE_SOURCES`` alone (seconds instead of the minute
+    the GEMV / GEMM sources take)."""
+    global _core
+    if _core is not None:
+        return _core
+    from .build import build_library, library_is_current
+
+    if _lib is not None or library_is_current():
+        _core = load()
+        return _core
+    path = build_library(sources_subset=_CORE_SOURCES, out=CORE_LIB_PATH)
+    _core = _bind(ctypes.CDLL(path), list(_CORE_SIGNATURES) + list(_CORE_SHARED))
+    return _core
+
+
 def exported_symbols() -> list[str]:
     return sorted(_SIGNATURES)
 
 
 def check(rc: int, what: str = "") -> None:
     if rc != 0:
-        msg = load().b200_last_error().decode(errors="replace")
+        msg = (_lib or _core or load()).b200_last_error().decode(errors="replace")
         if rc == 3:
             raise NotImplementedError(f"{what}: {msg}")
         raise B200Error(f"{what} failed (code {rc}): {msg}")

@@ -46,9 +46,21 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    srcs = sources()
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))] + [HEADER]
+def _headers() -> list[str]:
+    return [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))] + [HEADER]
+
+
+def library_is_current() -> bool:
+    """True when the full library exists and is newer than every source and header."""
+    return not _stale(LIB, sources() + _headers())
+
+
+def build_library(force: bool = False, verbose: bool = False, sources_subset: tuple[str, ...] | None = None, out: str | None = None) -> str:
+    """Build the full library, or -- with ``sources_subset`` (file names under csrc/) and ``out`` -- a library of those sources
+    only.  Objects are shared between the two, so neither build repeats the other's compilations."""
+    srcs = sources() if sources_subset is None else [os.path.join(CSRC, f) for f in sources_subset]
+    LIB = out or globals()["LIB"]
+    headers = _headers()
     if not force and not _stale(LIB, srcs + headers):
         return LIB
     nvcc = _nvcc()
@@ -66,10 +78,12 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs]
+    tmp = f"{LIB}.{os.getpid()}.tmp"   # link beside the target, then rename: a concurrent reader never sees half a library
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp, *objs]
     if verbose:
         print(" ".join(cmd), file=sys.stderr)
     subprocess.check_call(cmd)
+    os.replace(tmp, LIB)
     return LIB
 
 

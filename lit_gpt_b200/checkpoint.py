@@ -80,3 +80,43 @@ def load_quantized(model: nn.Module, path: Union[str, os.PathLike], device: Unio
         else:
             raise B200Error(f"unexpected tensor {k!r} in the checkpoint")
     return model
+
+
+# ---------------------------------------------------------------------------------------------------------
+# safetensors
+# ---------------------------------------------------------------------------------------------------------
+_SAFETENSORS_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F64": torch.float64,
+                       "I64": torch.int64, "I32": torch.int32, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8, "BOOL": torch.bool}
+
+
+def read_safetensors(path: Union[str, os.PathLike]) -> Dict[str, torch.Tensor]:
+    """Read a ``.safetensors`` file into CPU tensors: an 8-byte little-endian header length, that many bytes of JSON
+    (name -> dtype, shape, data_offsets relative to the end of the header), then the raw little-endian data."""
+    import json
+    import struct
+
+    with open(path, "rb") as fp:
+        raw = fp.read()
+    if len(raw) < 8:
+        raise B200Error(f"{path}: not a safetensors file")
+    (n,) = struct.unpack("<Q", raw[:8])
+    if 8 + n > len(raw):
+        raise B200Error(f"{path}: header length {n} exceeds the file")
+    header = json.loads(raw[8 : 8 + n].decode("utf-8"))
+    data = memoryview(raw)[8 + n :]
+    out: Dict[str, torch.Tensor] = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        dtype = _SAFETENSORS_DTYPES.get(info["dtype"])
+        if dtype is None:
+            raise B200Error(f"{path}: tensor {name!r} has unsupported dtype {info['dtype']}")
+        lo, hi = info["data_offsets"]
+        shape = tuple(int(s) for s in info["shape"])
+        count = 1
+        for s in shape:
+            count *= s
+        if hi - lo != count * torch.empty((), dtype=dtype).element_size() or hi > len(data):
+            raise B200Error(f"{path}: tensor {name!r} has inconsistent offsets")
+        out[name] = (torch.frombuffer(bytearray(data[lo:hi]), dtype=dtype).reshape(shape) if count else torch.empty(shape, dtype=dtype))
+    return out

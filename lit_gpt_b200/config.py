@@ -179,3 +179,130 @@ for _kind, _hf in (("", "-intermediate-step-1431k-3T"), ("-chat", "-Chat-v1.0"))
          padding_multiple=64, n_layer=22, n_head=32, n_embd=2048, n_query_groups=4, intermediate_size=5632, **_LLAMA)
 
 name_to_config: Dict[str, Dict[str, Any]] = {c["name"]: c for c in configs}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Architectures described by a nested ``config.json`` (a list of layers, each with a mixer and an optional feed-forward)
+# instead of the flat ``lit_config.json`` above.  ``load_config`` picks the configuration class by the file a checkpoint
+# directory holds and its "architecture" key; ``model_class`` maps a configuration to the module that runs it.
+# ---------------------------------------------------------------------------------------------------------
+@dataclass
+class LatentMixerSpec:
+    """Latent attention: queries through a q_rank bottleneck, keys / values up-projected per head from a cached kv_rank latent."""
+
+    heads: int
+    dim: int                       # query-key size per head
+    vdim: int                      # value size per head
+    kv_rank: int
+    q_rank: int
+    scale: float                   # multiplies q . k
+    kv_from: Optional[int] = None  # attend over that layer's cached latents instead of projecting own ones
+
+
+@dataclass
+class MoESpec:
+    """Sparse experts with a sigmoid router: `top` of `experts` per token, chosen among the `keep` best of `groups` groups."""
+
+    experts: int
+    top: int
+    ff: int
+    groups: int = 1
+    keep: int = 1
+
+
+@dataclass
+class LayerSpec:
+    type: str
+    mixer: LatentMixerSpec
+    mlp: Optional[MoESpec] = None
+
+
+@dataclass
+class PomipelConfig:
+    """Pomipel: learned absolute positions, post-normed blocks (x += norm(branch(x)) with zero-centred norm weights) of latent
+    attention and sparse experts, fp32 residual stream, scaled embedding and scaled logits."""
+
+    name: str = "Pomipel"
+    vocab_size: int = 0
+    n_embd: int = 0
+    block_size: int = 0            # size of the position table
+    norm_eps: float = 1e-5
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    layers: List[LayerSpec] = field(default_factory=list)
+
+    def __post_init__(self) -> None:
+        self.padded_vocab_size = self.vocab_size
+        self.n_layer = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            if layer.type != "latent_attention":
+                raise ValueError(f"layer {i}: unknown mixer type {layer.type!r}")
+            src = layer.mixer.kv_from
+            if src is not None:
+                if not (0 <= src < i) or self.layers[src].mixer.kv_from is not None:
+                    raise ValueError(f"layer {i}: kv_from must name an earlier layer that projects its own latents")
+                if self.layers[src].mixer.kv_rank != layer.mixer.kv_rank:
+                    raise ValueError(f"layer {i}: kv_rank differs from that of layer {src}, whose latents it reads")
+            m = layer.mlp
+            if m is not None and (m.experts % m.groups or not 0 < m.keep <= m.groups or m.keep * (m.experts // m.groups) < m.top):
+                raise ValueError(f"layer {i}: expert groups {m.groups} / keep {m.keep} do not fit {m.experts} experts, top {m.top}")
+
+    @classmethod
+    def from_dict(cls, js: Dict[str, Any]) -> "PomipelConfig":
+        layers = []
+        for i, entry in enumerate(js["layers"]):
+            mx = entry["mixer"]
+            mixer = LatentMixerSpec(heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx["vdim"]), kv_rank=int(mx["kv_rank"]),
+                                    q_rank=int(mx["q_rank"]), scale=float(mx["scale"]),
+                                    kv_from=None if mx.get("kv_from") is None else int(mx["kv_from"]))
+            mlp = None
+            if entry.get("mlp") is not None:
+                ml = entry["mlp"]
+                if ml.get("kind", "moe") != "moe":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {ml.get('kind')!r}")
+                router, groups = ml["router"], ml["router"].get("groups") or {}
+                mlp = MoESpec(experts=int(router["experts"]), top=int(router["top"]), ff=int(ml["expert"]["ff"]),
+                              groups=int(groups.get("count", 1)), keep=int(groups.get("keep", groups.get("count", 1))))
+            layers.append(LayerSpec(type=entry["type"], mixer=mixer, mlp=mlp))
+        return cls(name=js.get("architecture", "Pomipel"), vocab_size=int(js["vocab"]), n_embd=int(js["width"]),
+                   block_size=int(js["max_positions"]), norm_eps=float(js["norm"]["eps"]),
+                   embedding_scale=float(js.get("embedding", {}).get("scale", 1.0)), logit_scale=float(js.get("logit_scale", 1.0)),
+                   layers=layers)
+
+    @classmethod
+    def from_json(cls, path: Union[str, Path]) -> "PomipelConfig":
+        with open(path, encoding="utf-8") as fp:
+            return cls.from_dict(json.load(fp))
+
+
+# "architecture" value of config.json -> (configuration class, "module:class" of the model)
+architectures: Dict[str, Any] = {"Pomipel": (PomipelConfig, "lit_gpt_b200.pomipel:Pomipel")}
+
+
+def load_config(checkpoint_dir: Union[str, Path], **kwargs: Any) -> Any:
+    """The configuration of a checkpoint directory: ``lit_config.json`` (-> Config, as ``Config.from_checkpoint``) or a
+    ``config.json`` whose "architecture" names an entry of ``architectures``."""
+    path = Path(checkpoint_dir)
+    if (path / "lit_config.json").is_file() or not (path / "config.json").is_file():
+        return Config.from_checkpoint(path, **kwargs)
+    with open(path / "config.json", encoding="utf-8") as fp:
+        js = json.load(fp)
+    arch = js.get("architecture")
+    if arch not in architectures:
+        raise ValueError(f"{str(path / 'config.json')!r}: unknown architecture {arch!r} (known: {sorted(architectures)})")
+    return architectures[arch][0].from_dict(js)
+
+
+def model_class(config: Any) -> Type:
+    """The module class that runs `config`: GPT for the flat configurations, else the registered class of its architecture."""
+    import importlib
+
+    if isinstance(config, Config):
+        from lit_gpt_b200.model import GPT
+
+        return GPT
+    for cfg_cls, target in architectures.values():
+        if isinstance(config, cfg_cls):
+            mod, _, name = target.partition(":")
+            return getattr(importlib.import_module(mod), name)
+    raise TypeError(f"no model is registered for {type(config).__name__}")

@@ -35,6 +35,14 @@ extern std::atomic<int> g_pdl;
     }                                                                                         \
   } while (0)
 
+// Run a statement with T bound to the element type of a bf16-or-fp32 entry point.
+#define B200_FLOAT_TYPES(dtype, T, ...)                                                \
+  do {                                                                                 \
+    if ((dtype) == B200_BF16) { using T = __nv_bfloat16; __VA_ARGS__; }                \
+    else if ((dtype) == B200_F32) { using T = float; __VA_ARGS__; }                    \
+    else { b200::set_error("dtype must be bf16 or fp32"); return B200_ERR_INVALID; }   \
+  } while (0)
+
 // Launch with the programmatic-dependent-launch attribute when enabled: the kernel may start while its
 // predecessor in the stream drains; it must execute griddep_wait() before touching the predecessor's outputs
 // and before its first global write.

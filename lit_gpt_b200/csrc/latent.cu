@@ -1,0 +1,383 @@
+// Latent attention: attention whose keys and values are up-projections of one small cached vector per position
+// (the "latent" c, r numbers), with no rotation.  Per head h: k = W_uk[h] c, v = W_uv[h] c, score = (q_h . k) * scale,
+// causal softmax in fp32.  Only c is cached, so a layer may attend over ANOTHER layer's latents with its own W_uk / W_uv.
+//
+// Two kernels families:
+//  * prefill (many query rows per sequence): K and V of the context are expanded by a matrix product outside; the kernel
+//    here is a tiled flash attention over ragged sequences with separate query-key and value sizes, any sizes, operands
+//    bf16 or fp32, all arithmetic fp32 (online softmax with a running maximum).
+//  * decode (one query row per sequence): the up-projections are absorbed -- q'_h = W_uk[h]^T q_h (r numbers), scores are
+//    q'_h . c_j over the cached latents, the probabilities average the latents themselves, and W_uv[h] is applied once to
+//    that average.  Work per cached position is 2 r MACs per head instead of re-expanding dk + dv numbers; the context is
+//    split over CTAs (split-K) and a second kernel merges the splits and applies W_uv.
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------------------------
+// prefill
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kLpBM = 64, kLpBN = 64, kLpDV = 128, kLpThreads = 256;
+
+// row pitch (floats) for a tile whose rows are read as float4 by lanes one row apart: a multiple of 4 with pitch/4 odd, so
+// that the eight lanes of a quarter-warp hit eight different 16-byte bank groups
+__host__ __device__ inline int conflict_free_pitch(int d) {
+  int p = (d + 3) & ~3;
+  if (((p >> 2) & 1) == 0) p += 4;
+  return p;
+}
+
+// seq: {first query row in the packed batch, number of query rows, position of the first query row,
+//       row of position 0 of this sequence in the expanded K / V buffers}
+template <typename T>
+__global__ void __launch_bounds__(kLpThreads) latent_prefill_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k,
+                                                                     int64_t ldk, const T* __restrict__ v, int64_t ldv,
+                                                                     const int4* __restrict__ seqs, T* __restrict__ out, int64_t ldo,
+                                                                     int n_head, int dk, int dv, float scale_log2) {
+  extern __shared__ __align__(16) float lp_smem[];
+  griddep_launch();
+  griddep_wait();
+  const int4 sq = seqs[blockIdx.z];
+  const int qstart = sq.x, qlen = sq.y, pos0 = sq.z, kvstart = sq.w;
+  const int r0 = (int)blockIdx.x * kLpBM;
+  if (r0 >= qlen) return;
+  const int nchunk = (dv + kLpDV - 1) / kLpDV;
+  const int h = (int)blockIdx.y / nchunk, c0 = ((int)blockIdx.y % nchunk) * kLpDV;
+  const int dvc = min(kLpDV, dv - c0);
+  const int dkp = conflict_free_pitch(dk);
+  constexpr int PP = kLpBN + 4;                       // pitch of the probability tile (68: 17 is odd)
+  float* const Qs = lp_smem;                          // [64][dkp]
+  float* const Ks = Qs + kLpBM * dkp;                 // [64][dkp]
+  float* const Vs = Ks + kLpBN * dkp;                 // [64][128]
+  float* const Ps = Vs + kLpBN * kLpDV;               // [64][68]
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+
+  // Q tile, pre-multiplied by scale * log2(e); rows past the sequence and the padding columns are zero
+  for (int idx = tid; idx < kLpBM * dkp; idx += kLpThreads) {
+    const int i = idx / dkp, d = idx - i * dkp;
+    float val = 0.f;
+    if (r0 + i < qlen && d < dk) val = load_as_float(q, (int64_t)(qstart + r0 + i) * ldq + (int64_t)h * dk + d) * scale_log2;
+    Qs[idx] = val;
+  }
+  const int last_row = min(r0 + kLpBM, qlen) - 1;
+  const int n_keys = pos0 + last_row + 1;             // keys 0 .. position of the tile's last valid row
+
+  float o[4][8];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) o[a][b] = 0.f;
+  float m_run[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l_run[4] = {0.f, 0.f, 0.f, 0.f};
+  int lim[4];                                         // last visible key of each of this thread's rows (-1: no row)
+#pragma unroll
+  for (int a = 0; a < 4; ++a) lim[a] = (r0 + ty + 16 * a < qlen) ? pos0 + r0 + ty + 16 * a : -1;
+
+  for (int j0 = 0; j0 < n_keys; j0 += kLpBN) {
+    __syncthreads();                                  // previous tile fully consumed (and Q visible on the first pass)
+    for (int idx = tid; idx < kLpBN * dkp; idx += kLpThreads) {
+      const int j = idx / dkp, d = idx - j * dkp;
+      float val = 0.f;
+      if (j0 + j < n_keys && d < dk) val = load_as_float(k, (int64_t)(kvstart + j0 + j) * ldk + (int64_t)h * dk + d);
+      Ks[idx] = val;
+    }
+    for (int idx = tid; idx < kLpBN * kLpDV; idx += kLpThreads) {
+      const int j = idx / kLpDV, c = idx - j * kLpDV;
+      float val = 0.f;
+      if (j0 + j < n_keys && c < dvc) val = load_as_float(v, (int64_t)(kvstart + j0 + j) * ldv + (int64_t)h * dv + c0 + c);
+      Vs[idx] = val;
+    }
+    __syncthreads();
+
+    // S = Q K^T for rows ty + 16 a, keys tx + 16 b
+    float s[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
+    for (int d = 0; d < dkp; d += 4) {
+      float4 qa[4], kb[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) qa[a] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * a) * dkp + d);
+#pragma unroll
+      for (int b = 0; b < 4; ++b) kb[b] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * b) * dkp + d);
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          s[a][b] = fmaf(qa[a].x, kb[b].x, s[a][b]);
+          s[a][b] = fmaf(qa[a].y, kb[b].y, s[a][b]);
+          s[a][b] = fmaf(qa[a].z, kb[b].z, s[a][b]);
+          s[a][b] = fmaf(qa[a].w, kb[b].w, s[a][b]);
+        }
+    }
+    // causal mask, running maximum, probabilities
+    float alpha[4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        if (j0 + tx + 16 * b > lim[a]) s[a][b] = -INFINITY;
+        mx = fmaxf(mx, s[a][b]);
+      }
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float m_new = fmaxf(m_run[a], mx);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[a] = exp2f(m_run[a] - m_safe);            // exp2(-inf) = 0 on the first tile
+      float ps = 0.f;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float p = exp2f(s[a][b] - m_safe);
+        ps += p;
+        Ps[(ty + 16 * a) * PP + tx + 16 * b] = p;
+      }
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+      l_run[a] = l_run[a] * alpha[a] + ps;
+      m_run[a] = m_new;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) o[a][b] *= alpha[a];
+    }
+    __syncthreads();
+    // O += P V for rows ty + 16 a, value columns 4 tx .. 4 tx + 3 and 64 + 4 tx .. 64 + 4 tx + 3
+    for (int j = 0; j < kLpBN; j += 4) {
+      float4 pa[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) pa[a] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * a) * PP + j);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const float4 v0 = *reinterpret_cast<const float4*>(Vs + (j + jj) * kLpDV + 4 * tx);
+        const float4 v1 = *reinterpret_cast<const float4*>(Vs + (j + jj) * kLpDV + 64 + 4 * tx);
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const float p = jj == 0 ? pa[a].x : jj == 1 ? pa[a].y : jj == 2 ? pa[a].z : pa[a].w;
+          o[a][0] = fmaf(p, v0.x, o[a][0]); o[a][1] = fmaf(p, v0.y, o[a][1]);
+          o[a][2] = fmaf(p, v0.z, o[a][2]); o[a][3] = fmaf(p, v0.w, o[a][3]);
+          o[a][4] = fmaf(p, v1.x, o[a][4]); o[a][5] = fmaf(p, v1.y, o[a][5]);
+          o[a][6] = fmaf(p, v1.z, o[a][6]); o[a][7] = fmaf(p, v1.w, o[a][7]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int i = r0 + ty + 16 * a;
+    if (i >= qlen) continue;
+    const float inv = 1.0f / l_run[a];
+    T* orow = out + (int64_t)(qstart + i) * ldo + (int64_t)h * dv + c0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const int c = (b < 4 ? 0 : 64) + 4 * tx + (b & 3);
+      if (c < dvc) store_from_float(orow, c, o[a][b] * inv);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// decode
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kLdThreads = 128, kLdTile = 32, kLdMaxRPT = 8;   // latent size <= 128 * 8
+
+// grid (n_split, n_head, batch).  Partial result of one split: r unnormalised latent sums, then the running maximum
+// (log2 domain) and the probability sum.
+template <typename T>
+__global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ w_uk,
+                                                                          const T* __restrict__ cache, int64_t slot_stride,
+                                                                          const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                                                                          float* __restrict__ ws, int n_head, int dk, int r,
+                                                                          float scale_log2, int max_seq) {
+  extern __shared__ __align__(16) unsigned char ld_smem_raw[];
+  griddep_launch();
+  griddep_wait();
+  float* const qs = reinterpret_cast<float*>(ld_smem_raw);   // [dk]
+  float* const ql = qs + dk;                                   // [r]  q' = scale * W_uk[h]^T q
+  float* const sc = ql + r;                                    // [32] scores, then probabilities
+  float* const st = sc + kLdTile;                              // [4]  running max, sum, rescale factor
+  T* const cs = reinterpret_cast<T*>(st + 4);                  // [32][r]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int split = blockIdx.x, n_split = gridDim.x, h = blockIdx.y, b = blockIdx.z;
+  int ctx = row_pos[b] + 1;
+  ctx = ctx < 1 ? 1 : (ctx > max_seq ? max_seq : ctx);
+  int per = (ctx + n_split - 1) / n_split;
+  per = (per + kLdTile - 1) / kLdTile * kLdTile;
+  const int k0 = split * per, k1 = min(ctx, k0 + per);
+  const T* crow = cache + (int64_t)row_slot[b] * slot_stride;
+
+  for (int d = tid; d < dk; d += kLdThreads) qs[d] = load_as_float(q, (int64_t)b * ldq + (int64_t)h * dk + d);
+  if (tid == 0) { st[0] = -INFINITY; st[1] = 0.f; st[2] = 1.f; }
+  __syncthreads();
+  for (int rr = tid; rr < r; rr += kLdThreads) {
+    float acc = 0.f;
+    for (int d = 0; d < dk; ++d) acc = fmaf(qs[d], load_as_float(w_uk, ((int64_t)h * dk + d) * r + rr), acc);
+    ql[rr] = acc * scale_log2;
+  }
+  float o[kLdMaxRPT];
+#pragma unroll
+  for (int i = 0; i < kLdMaxRPT; ++i) o[i] = 0.f;
+
+  for (int j0 = k0; j0 < k1; j0 += kLdTile) {
+    __syncthreads();   // previous tile consumed; ql visible on the first pass
+    const int nj = min(kLdTile, k1 - j0);
+    for (int idx = tid; idx < nj * r; idx += kLdThreads) cs[idx] = crow[(int64_t)j0 * r + idx];
+    __syncthreads();
+    for (int j = warp; j < kLdTile; j += kLdThreads / 32) {
+      float dot = 0.f;
+      if (j < nj)
+        for (int rr = lane; rr < r; rr += 32) dot = fmaf(ql[rr], load_as_float(cs, (int64_t)j * r + rr), dot);
+      dot = warp_sum(dot);
+      if (lane == 0) sc[j] = j < nj ? dot : -INFINITY;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const float sv = sc[lane];
+      const float m_old = st[0];
+      const float m_new = fmaxf(m_old, warp_max(sv));   // finite: every tile holds at least one key
+      const float p = exp2f(sv - m_new);
+      const float psum = warp_sum(p);
+      __syncwarp();
+      sc[lane] = p;
+      if (lane == 0) {
+        const float a = exp2f(m_old - m_new);
+        st[2] = a;
+        st[1] = st[1] * a + psum;
+        st[0] = m_new;
+      }
+    }
+    __syncthreads();
+    const float a = st[2];
+#pragma unroll
+    for (int i = 0; i < kLdMaxRPT; ++i) {
+      const int rr = tid + i * kLdThreads;
+      if (rr < r) {
+        float acc = o[i] * a;
+        for (int j = 0; j < nj; ++j) acc = fmaf(sc[j], load_as_float(cs, (int64_t)j * r + rr), acc);
+        o[i] = acc;
+      }
+    }
+  }
+  __syncthreads();
+  float* dst = ws + (((int64_t)b * n_head + h) * n_split + split) * (r + 2);
+#pragma unroll
+  for (int i = 0; i < kLdMaxRPT; ++i) {
+    const int rr = tid + i * kLdThreads;
+    if (rr < r) dst[rr] = o[i];
+  }
+  if (tid == 0) { dst[r] = st[0]; dst[r + 1] = st[1]; }
+}
+
+// grid (n_head, batch): merge the splits, then out_h = W_uv[h] (sum_j p_j c_j)
+template <typename T>
+__global__ void __launch_bounds__(kLdThreads) latent_decode_merge_kernel(const float* __restrict__ ws, const T* __restrict__ w_uv,
+                                                                          T* __restrict__ out, int64_t ldo, int n_head, int dv, int r,
+                                                                          int n_split) {
+  extern __shared__ __align__(16) float lm_smem[];   // [r] averaged latent, [n_split] weights
+  griddep_launch();
+  griddep_wait();
+  float* const avg = lm_smem;
+  float* const wgt = avg + r;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float* src = ws + ((int64_t)b * n_head + h) * n_split * (r + 2);
+  float mx = -INFINITY;
+  for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, src[(int64_t)s * (r + 2) + r]);
+  float tot = 0.f;
+  for (int s = 0; s < n_split; ++s) {
+    const float m = src[(int64_t)s * (r + 2) + r];
+    const float w = m == -INFINITY ? 0.f : exp2f(m - mx);
+    tot = fmaf(w, src[(int64_t)s * (r + 2) + r + 1], tot);
+    if (tid == 0) wgt[s] = w;
+  }
+  __syncthreads();
+  const float inv = 1.0f / tot;
+  for (int rr = tid; rr < r; rr += kLdThreads) {
+    float acc = 0.f;
+    for (int s = 0; s < n_split; ++s) acc = fmaf(wgt[s], src[(int64_t)s * (r + 2) + rr], acc);
+    avg[rr] = acc * inv;
+  }
+  __syncthreads();
+  for (int c = warp; c < dv; c += kLdThreads / 32) {
+    const T* wr = w_uv + ((int64_t)h * dv + c) * r;
+    float dot = 0.f;
+    for (int rr = lane; rr < r; rr += 32) dot = fmaf(load_as_float(wr, rr), avg[rr], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) store_from_float(out, (int64_t)b * ldo + (int64_t)h * dv + c, dot);
+  }
+}
+
+template <typename T>
+int prefill_launch(const b200_latent_prefill_args* a, cudaStream_t st) {
+  const int dkp = conflict_free_pitch(a->dk);
+  const size_t smem = (size_t)(2 * kLpBM * dkp + kLpBN * kLpDV + kLpBM * (kLpBN + 4)) * sizeof(float);
+  B200_CHECK_ARG(smem <= 227 * 1024, "b200_latent_prefill: query-key size %d needs %zu bytes of shared memory", a->dk, smem);
+  static PerDeviceOnce once;
+  if (once.need()) {
+    B200_CUDA(cudaFuncSetAttribute(latent_prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    once.done();
+  }
+  const int nchunk = (a->dv + kLpDV - 1) / kLpDV;
+  const dim3 grid((unsigned)((a->max_q_len + kLpBM - 1) / kLpBM), (unsigned)(a->n_head * nchunk), (unsigned)a->n_seqs);
+  B200_CUDA(launch(latent_prefill_kernel<T>, grid, dim3(kLpThreads), smem, st, (const T*)a->q, a->ldq, (const T*)a->k, a->ldk, (const T*)a->v,
+                   a->ldv, (const int4*)a->seqs, (T*)a->out, a->ldo, a->n_head, a->dk, a->dv, a->scale * 1.4426950408889634f));
+  return B200_OK;
+}
+
+template <typename T>
+int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
+  const size_t smem1 = (size_t)(a->dk + a->r + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * a->r * sizeof(T);
+  const size_t smem2 = (size_t)(a->r + a->n_split) * sizeof(float);
+  B200_CHECK_ARG(smem1 <= 227 * 1024 && smem2 <= 227 * 1024, "b200_latent_decode: sizes need too much shared memory");
+  static PerDeviceOnce once;
+  if (once.need()) {
+    B200_CUDA(cudaFuncSetAttribute(latent_decode_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(latent_decode_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    once.done();
+  }
+  B200_CUDA(launch(latent_decode_split_kernel<T>, dim3((unsigned)a->n_split, (unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem1, st,
+                   (const T*)a->q, a->ldq, (const T*)a->w_uk, (const T*)a->cache, a->slot_stride, a->row_slot, a->row_pos, (float*)a->workspace,
+                   a->n_head, a->dk, a->r, a->scale * 1.4426950408889634f, a->max_seq));
+  B200_CUDA(launch(latent_decode_merge_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem2, st,
+                   (const float*)a->workspace, (const T*)a->w_uv, (T*)a->out, a->ldo, a->n_head, a->dv, a->r, a->n_split));
+  return B200_OK;
+}
+
+}  // namespace
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_latent_prefill(const b200_latent_prefill_args* a, b200_stream_t stream) {
+  B200_CHECK_ARG(a && a->q && a->k && a->v && a->seqs && a->out, "b200_latent_prefill: null pointer");
+  B200_CHECK_ARG(a->n_seqs > 0 && a->n_seqs <= 65535 && a->max_q_len > 0 && a->n_head > 0 && a->dk > 0 && a->dv > 0,
+                 "b200_latent_prefill: bad shape");
+  B200_CHECK_ARG((int64_t)a->n_head * ((a->dv + kLpDV - 1) / kLpDV) <= 65535, "b200_latent_prefill: too many heads");
+  if (a->dtype == B200_BF16) return prefill_launch<__nv_bfloat16>(a, (cudaStream_t)stream);
+  if (a->dtype == B200_F32) return prefill_launch<float>(a, (cudaStream_t)stream);
+  set_error("b200_latent_prefill: dtype must be bf16 or fp32");
+  return B200_ERR_INVALID;
+}
+
+size_t b200_latent_decode_workspace_bytes(int batch, int n_head, int r, int n_split) {
+  return (size_t)batch * n_head * n_split * (r + 2) * sizeof(float);
+}
+
+int b200_latent_decode(const b200_latent_decode_args* a, b200_stream_t stream) {
+  B200_CHECK_ARG(a && a->q && a->w_uk && a->w_uv && a->cache && a->row_slot && a->row_pos && a->out && a->workspace,
+                 "b200_latent_decode: null pointer");
+  B200_CHECK_ARG(a->batch > 0 && a->batch <= 65535 && a->n_head > 0 && a->n_head <= 65535 && a->dk > 0 && a->dv > 0 && a->r > 0 && a->n_split > 0,
+                 "b200_latent_decode: bad shape");
+  B200_CHECK_ARG(a->r <= kLdThreads * kLdMaxRPT, "b200_latent_decode: latent size %d above %d", a->r, kLdThreads * kLdMaxRPT);
+  B200_CHECK_ARG(a->workspace_bytes >= b200_latent_decode_workspace_bytes(a->batch, a->n_head, a->r, a->n_split),
+                 "b200_latent_decode: workspace too small");
+  if (a->dtype == B200_BF16) return decode_launch<__nv_bfloat16>(a, (cudaStream_t)stream);
+  if (a->dtype == B200_F32) return decode_launch<float>(a, (cudaStream_t)stream);
+  set_error("b200_latent_decode: dtype must be bf16 or fp32");
+  return B200_ERR_INVALID;
+}
+
+}  // extern "C"

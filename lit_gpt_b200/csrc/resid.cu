@@ -1,0 +1,186 @@
+// Glue kernels for models that keep the residual stream in fp32 beside a working copy in the matrix-product dtype
+// (bf16 or fp32): token + position embedding, RMS norms over strided / gathered / scattered rows (statistics always in
+// fp32), the "x += norm(branch)" residual update of post-normed blocks, a row gather and the logit scale.
+// One CTA per row; rows are a few hundred to a few thousand elements, so these are launch- and latency-bound.
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kRowThreads = 128;
+
+// sum over the CTA (kRowThreads threads); every thread gets the result
+__device__ __forceinline__ float cta_sum(float v, float* s_part) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();  // s_part may still be read from a previous call
+  if (lane == 0) s_part[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < kRowThreads / 32; ++w) t += s_part[w];
+  return t;
+}
+
+// x[row] = embed[token[row]] * scale + pos_table[pos[row]]  (fp32), act[row] = T(x[row])
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) embed_pos_kernel(const int* __restrict__ tokens, const int* __restrict__ pos,
+                                                                 const T* __restrict__ embed, const T* __restrict__ pos_table,
+                                                                 float scale, float* __restrict__ x, T* __restrict__ act, int d,
+                                                                 int vocab, int max_pos) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t row = blockIdx.x;
+  int tok = tokens[row];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // never read out of bounds
+  const T* e = embed + (int64_t)tok * d;
+  const T* p = nullptr;
+  if (pos_table) {
+    int pp = pos[row];
+    pp = pp < 0 ? 0 : (pp >= max_pos ? max_pos - 1 : pp);
+    p = pos_table + (int64_t)pp * d;
+  }
+  for (int i = threadIdx.x; i < d; i += kRowThreads) {
+    float v = load_as_float(e, i) * scale;
+    if (p) v += load_as_float(p, i);
+    x[row * d + i] = v;
+    store_from_float(act, row * d + i, v);
+  }
+}
+
+// out[orow] = in[irow] / sqrt(mean(in[irow]^2) + eps) * (weight or 1 + weight); blockIdx.y picks one of two segments so
+// that the two norms that follow one fused down-projection run as a single launch
+struct RmsSeg {
+  const void* in;
+  const void* weight;
+  void* out;
+  const int64_t* in_rows;   // NULL: row index itself
+  const int64_t* out_rows;  // NULL: row index itself
+  int64_t ld_in, ld_out;
+  int d, plus_one;
+};
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(kRowThreads) rms_rows_kernel(RmsSeg s0, RmsSeg s1, float eps) {
+  __shared__ float s_part[kRowThreads / 32];
+  griddep_launch();
+  griddep_wait();
+  const RmsSeg s = blockIdx.y == 0 ? s0 : s1;
+  const int64_t row = blockIdx.x;
+  const int64_t irow = s.in_rows ? s.in_rows[row] : row, orow = s.out_rows ? s.out_rows[row] : row;
+  if (orow < 0) return;   // a row with nowhere to go (padding)
+  const TI* xr = reinterpret_cast<const TI*>(s.in) + irow * s.ld_in;
+  const TO* w = reinterpret_cast<const TO*>(s.weight);
+  TO* yr = reinterpret_cast<TO*>(s.out) + orow * s.ld_out;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < s.d; i += kRowThreads) {
+    const float v = load_as_float(xr, i);
+    ss = fmaf(v, v, ss);
+  }
+  const float rstd = 1.0f / sqrtf(cta_sum(ss, s_part) / (float)s.d + eps);
+  for (int i = threadIdx.x; i < s.d; i += kRowThreads) {
+    const float g = load_as_float(w, i) + (s.plus_one ? 1.0f : 0.0f);
+    store_from_float(yr, i, load_as_float(xr, i) * rstd * g);
+  }
+}
+
+// x[row] += y[row] / sqrt(mean(y[row]^2) + eps) * (1 + w);  act[row] = T(x[row]).  x stays fp32.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) residual_norm_add_kernel(const T* __restrict__ y, const T* __restrict__ w, float eps,
+                                                                         float* __restrict__ x, T* __restrict__ act, int d) {
+  __shared__ float s_part[kRowThreads / 32];
+  griddep_launch();
+  griddep_wait();
+  const int64_t row = blockIdx.x;
+  const T* yr = y + row * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += kRowThreads) {
+    const float v = load_as_float(yr, i);
+    ss = fmaf(v, v, ss);
+  }
+  const float rstd = 1.0f / sqrtf(cta_sum(ss, s_part) / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += kRowThreads) {
+    const float v = x[row * d + i] + load_as_float(yr, i) * rstd * (1.0f + load_as_float(w, i));
+    x[row * d + i] = v;
+    store_from_float(act, row * d + i, v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(const T* __restrict__ src, const int64_t* __restrict__ rows,
+                                                                   T* __restrict__ dst, int d) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t r = rows[blockIdx.x];
+  for (int i = threadIdx.x; i < d; i += kRowThreads) dst[(int64_t)blockIdx.x * d + i] = src[r * d + i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) scale_f32_kernel(const T* __restrict__ in, float scale, float* __restrict__ out, int64_t n) {
+  griddep_launch();
+  griddep_wait();
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) out[i] = load_as_float(in, i) * scale;
+}
+
+}  // namespace
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_embed_pos(const int32_t* tokens, const int32_t* pos, const void* embed, const void* pos_table, float scale, float* x,
+                   void* act, int64_t rows, int d, int vocab, int max_pos, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(tokens && embed && x && act && (pos || !pos_table), "b200_embed_pos: null pointer");
+  B200_CHECK_ARG(rows > 0 && rows <= 0x7fffffff && d > 0 && vocab > 0, "b200_embed_pos: bad shape");
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(embed_pos_kernel<T>, dim3((unsigned)rows), dim3(kRowThreads), 0, (cudaStream_t)stream, tokens,
+                                               pos, (const T*)embed, (const T*)pos_table, scale, x, (T*)act, d, vocab, max_pos)));
+  return B200_OK;
+}
+
+int b200_rms_rows(const b200_rms_rows_seg* segs, int n_segs, int64_t rows, float eps, int in_dtype, int out_dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(segs && (n_segs == 1 || n_segs == 2), "b200_rms_rows: one or two segments");
+  B200_CHECK_ARG(rows > 0 && rows <= 0x7fffffff, "b200_rms_rows: bad row count");
+  RmsSeg s[2];
+  for (int i = 0; i < 2; ++i) {
+    const b200_rms_rows_seg& a = segs[i < n_segs ? i : 0];
+    B200_CHECK_ARG(a.in && a.weight && a.out && a.d > 0, "b200_rms_rows: null pointer or empty row");
+    s[i] = RmsSeg{a.in, a.weight, a.out, a.in_rows, a.out_rows, a.ld_in, a.ld_out, a.d, a.plus_one};
+  }
+  const dim3 grid((unsigned)rows, (unsigned)n_segs), block(kRowThreads);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == B200_BF16 && out_dtype == B200_BF16) B200_CUDA(launch(rms_rows_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, st, s[0], s[1], eps));
+  else if (in_dtype == B200_F32 && out_dtype == B200_BF16) B200_CUDA(launch(rms_rows_kernel<float, __nv_bfloat16>, grid, block, 0, st, s[0], s[1], eps));
+  else if (in_dtype == B200_F32 && out_dtype == B200_F32) B200_CUDA(launch(rms_rows_kernel<float, float>, grid, block, 0, st, s[0], s[1], eps));
+  else { set_error("b200_rms_rows: unsupported dtype pair"); return B200_ERR_INVALID; }
+  return B200_OK;
+}
+
+int b200_residual_norm_add(const void* y, const void* weight, float eps, float* x, void* act, int64_t rows, int d, int dtype,
+                           b200_stream_t stream) {
+  B200_CHECK_ARG(y && weight && x && act, "b200_residual_norm_add: null pointer");
+  B200_CHECK_ARG(rows > 0 && rows <= 0x7fffffff && d > 0, "b200_residual_norm_add: bad shape");
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(residual_norm_add_kernel<T>, dim3((unsigned)rows), dim3(kRowThreads), 0, (cudaStream_t)stream,
+                                               (const T*)y, (const T*)weight, eps, x, (T*)act, d)));
+  return B200_OK;
+}
+
+int b200_gather_rows(const void* src, const int64_t* rows, void* dst, int64_t n_rows, int d, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(src && rows && dst && n_rows > 0 && n_rows <= 0x7fffffff && d > 0, "b200_gather_rows: bad argument");
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(gather_rows_kernel<T>, dim3((unsigned)n_rows), dim3(kRowThreads), 0, (cudaStream_t)stream,
+                                               (const T*)src, rows, (T*)dst, d)));
+  return B200_OK;
+}
+
+int b200_scale_f32(const void* in, float scale, float* out, int64_t n, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(in && out && n > 0, "b200_scale_f32: bad argument");
+  int64_t blocks = (n + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(scale_f32_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)in, scale, out, n)));
+  return B200_OK;
+}
+
+}  // extern "C"

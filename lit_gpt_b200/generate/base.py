@@ -82,7 +82,7 @@ class DecodeGraph:
     """One captured decode step: token/pos/history live on the device; ``replay()`` advances one token."""
 
     def __init__(self, model: GPT, temperature: float, top_k: Optional[int], dtype: torch.dtype) -> None:
-        dev = model.transformer.wte.weight.device
+        dev = next(model.parameters()).device
         self.model, self.temperature, self.top_k = model, temperature, top_k
         self.token = torch.zeros(1, dtype=dtype, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
@@ -93,7 +93,7 @@ class DecodeGraph:
 
     def _step(self) -> None:
         logits = self.model(self.token.view(1, 1), self.pos)
-        if self.temperature == 0.0 and self.top_k is None:
+        if self.temperature == 0.0 and self.top_k is None and logits.dtype == torch.bfloat16:
             K.argmax_(logits, self.token, pos_inout=self.pos, history=self.history)  # greedy: fused argmax + bookkeeping
         else:  # stochastic: the fused sampler draws, advances its Philox offset and does the same bookkeeping
             K.sample_(logits, self.token, self.temperature, self.top_k, self.rng, pos_inout=self.pos, history=self.history)
@@ -156,6 +156,10 @@ class PrefillGraph:
 
 def _graph_key(model: GPT) -> Tuple:
     # a captured graph bakes in raw device pointers: key on the addresses themselves (id() of a freed tensor can be reused)
+    if hasattr(model, "graph_key"):   # models with caches of their own kind name their pinned buffers themselves
+        dev = model.device
+        rng = _rng_for(dev).data_ptr() if dev.type == "cuda" else 0
+        return model.graph_key() + (rng,)
     kv = [(b.attn.kv_cache.k.data_ptr(), b.attn.kv_cache.v.data_ptr()) for b in model.transformer.h]
     dev = model.transformer.wte.weight.device
     rng = _rng_for(dev).data_ptr() if dev.type == "cuda" else 0   # the sampler state's address is baked in too
@@ -203,7 +207,8 @@ def generate(model: GPT, prompt: torch.Tensor, max_returned_tokens: int, *, temp
         _rng_for(device)   # apply a pending reseed before any draw of this call
     tokens = [prompt]
     input_pos = torch.tensor([T], device=device)
-    if (1 < T <= PREFILL_GRAPH_MAX_T and prompt.is_cuda and getattr(model, "tp_world_size", 1) == 1 and not model.spans_devices()
+    if (1 < T <= PREFILL_GRAPH_MAX_T and prompt.is_cuda and getattr(model, "supports_prefill_graph", True)
+            and getattr(model, "tp_world_size", 1) == 1 and not model.spans_devices()
             and model.fused_decode_ready(prompt.view(1, -1)) and model.config.intermediate_size % 8 == 0):
         pg = _prefill_graph_for(model, T, temperature, top_k, prompt.dtype)
         pg.prompt.copy_(prompt.view(1, -1))

@@ -574,3 +574,156 @@ def launch_count() -> int:
 def qgemv_tune(ksteps: int = 0, ctas_per_sm: int = 0, force_generic: bool = False) -> None:
     C.load().b200_qgemv_tune(ksteps, ctas_per_sm, int(force_generic))
 
+
+
+# ---------------------------------------------------------------------------------------------------------
+# fp32 residual stream, latent attention, sparse experts (csrc/resid.cu, latent.cu, moe.cu).  `T` below is the
+# matrix-product dtype of a model: bfloat16 or float32; these wrappers load only the core library (C.load_core).
+# ---------------------------------------------------------------------------------------------------------
+def _code(t: torch.Tensor) -> int:
+    if t.dtype not in (torch.bfloat16, torch.float32):
+        raise C.B200Error(f"expected a bfloat16 or float32 tensor (got {t.dtype})")
+    return C.DTYPE_CODE[t.dtype]
+
+
+def embed_pos(tokens: torch.Tensor, pos: torch.Tensor, embed: torch.Tensor, pos_table: Optional[torch.Tensor], scale: float):
+    """tokens, pos int32 (n,) -> (x fp32 (n, d), act T (n, d)) with x = embed[tokens] * scale + pos_table[pos]."""
+    C.require_cuda(tokens, pos, embed, pos_table)
+    if tokens.dtype != torch.int32 or pos.dtype != torch.int32:
+        raise C.B200Error("embed_pos: tokens and pos must be int32")
+    n, d = tokens.numel(), embed.shape[1]
+    x = torch.empty((n, d), dtype=torch.float32, device=embed.device)
+    act = torch.empty((n, d), dtype=embed.dtype, device=embed.device)
+    C.check(C.load_core().b200_embed_pos(tokens.data_ptr(), pos.data_ptr(), embed.data_ptr(), C.ptr(pos_table), float(scale), x.data_ptr(),
+                                         act.data_ptr(), n, d, embed.shape[0], 0 if pos_table is None else pos_table.shape[0], _code(embed),
+                                         C.stream_ptr(embed.device)), "embed_pos")
+    return x, act
+
+
+def _seg(inp: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, d: int, plus_one: bool, in_rows=None, out_rows=None) -> "C.RmsRowsSeg":
+    if inp.stride(-1) != 1 or out.stride(-1) != 1 or not weight.is_contiguous():
+        raise C.B200Error("rms_rows: rows must be contiguous")
+    for idx in (in_rows, out_rows):
+        if idx is not None and (idx.dtype != torch.int64 or not idx.is_contiguous()):
+            raise C.B200Error("rms_rows: row indices must be contiguous int64")
+    return C.RmsRowsSeg(inp=inp.data_ptr(), weight=weight.data_ptr(), out=out.data_ptr(), in_rows=C.ptr(in_rows), out_rows=C.ptr(out_rows),
+                        ld_in=inp.stride(-2), ld_out=out.stride(-2), d=d, plus_one=int(plus_one))
+
+
+def rms_rows(rows: int, eps: float, *segs: "C.RmsRowsSeg", in_dtype: torch.dtype, out_dtype: torch.dtype, device: torch.device) -> None:
+    """One launch normalising `rows` rows of one or two segments built by ``rms_seg`` (statistics in fp32)."""
+    arr = (C.RmsRowsSeg * len(segs))(*segs)
+    C.check(C.load_core().b200_rms_rows(arr, len(segs), rows, float(eps), C.DTYPE_CODE[in_dtype], C.DTYPE_CODE[out_dtype], C.stream_ptr(device)),
+            "rms_rows")
+
+
+rms_seg = _seg
+
+
+def residual_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor, act: torch.Tensor) -> None:
+    """x (fp32, in place) += y / rms(y) * (1 + weight); act = T(x)."""
+    C.require_cuda(y, weight, x, act)
+    if x.dtype != torch.float32 or not (y.is_contiguous() and x.is_contiguous() and act.is_contiguous()) or act.dtype != y.dtype:
+        raise C.B200Error("residual_norm_add: x must be fp32, y and act of one dtype, all contiguous")
+    d = y.shape[-1]
+    C.check(C.load_core().b200_residual_norm_add(y.data_ptr(), weight.data_ptr(), float(eps), x.data_ptr(), act.data_ptr(), y.numel() // d, d,
+                                                 _code(y), C.stream_ptr(y.device)), "residual_norm_add")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    C.require_cuda(src, rows)
+    if not src.is_contiguous() or rows.dtype != torch.int64:
+        raise C.B200Error("gather_rows: contiguous source and int64 rows")
+    d = src.shape[-1]
+    dst = torch.empty((rows.numel(), d), dtype=src.dtype, device=src.device)
+    C.check(C.load_core().b200_gather_rows(src.data_ptr(), rows.data_ptr(), dst.data_ptr(), rows.numel(), d, _code(src), C.stream_ptr(src.device)),
+            "gather_rows")
+    return dst
+
+
+def scale_f32(t: torch.Tensor, scale: float) -> torch.Tensor:
+    C.require_cuda(t)
+    t = t.contiguous()
+    out = torch.empty(t.shape, dtype=torch.float32, device=t.device)
+    C.check(C.load_core().b200_scale_f32(t.data_ptr(), float(scale), out.data_ptr(), t.numel(), _code(t), C.stream_ptr(t.device)), "scale_f32")
+    return out
+
+
+def latent_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqs: torch.Tensor, max_q_len: int, n_head: int, dk: int, dv: int,
+                   scale: float) -> torch.Tensor:
+    """Ragged causal attention without rotation.  q (n, H * dk); k (m, H * dk) and v (m, H * dv) may be column slices of one
+    buffer; seqs int32 (S, 4) = first query row, query rows, position of the first query row, row of position 0 in k / v."""
+    C.require_cuda(q, k, v, seqs)
+    if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
+        raise C.B200Error("latent_prefill: seqs must be contiguous int32 (S, 4)")
+    if not (q.dtype == k.dtype == v.dtype) or q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1:
+        raise C.B200Error("latent_prefill: q, k, v of one dtype with unit inner stride")
+    out = torch.empty((q.shape[0], n_head * dv), dtype=q.dtype, device=q.device)
+    args = C.LatentPrefillArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
+                               ldo=out.stride(0), seqs=seqs.data_ptr(), n_seqs=seqs.shape[0], max_q_len=max_q_len, n_head=n_head, dk=dk, dv=dv,
+                               scale=float(scale), dtype=_code(q))
+    C.check(C.load_core().b200_latent_prefill(ctypes.byref(args), C.stream_ptr(q.device)), "latent_prefill")
+    return out
+
+
+def latent_decode(q: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, cache: torch.Tensor, row_slot: torch.Tensor, row_pos: torch.Tensor,
+                  n_head: int, dk: int, dv: int, scale: float, n_split: int) -> torch.Tensor:
+    """One query row per sequence over the cached latents (slots, max_seq, r); row b reads positions 0 .. row_pos[b] of slot
+    row_slot[b].  Returns (B, H * dv)."""
+    C.require_cuda(q, w_uk, w_uv, cache, row_slot, row_pos)
+    if row_slot.dtype != torch.int32 or row_pos.dtype != torch.int32:
+        raise C.B200Error("latent_decode: row_slot and row_pos must be int32")
+    if not (q.dtype == w_uk.dtype == w_uv.dtype == cache.dtype) or not (w_uk.is_contiguous() and w_uv.is_contiguous() and cache.is_contiguous()):
+        raise C.B200Error("latent_decode: one dtype, contiguous weights and cache")
+    B, r, max_seq = q.shape[0], cache.shape[-1], cache.shape[1]
+    lib = C.load_core()
+    ws = _ws("latent", q.device, lib.b200_latent_decode_workspace_bytes(B, n_head, r, n_split))
+    out = torch.empty((B, n_head * dv), dtype=q.dtype, device=q.device)
+    args = C.LatentDecodeArgs(q=q.data_ptr(), w_uk=w_uk.data_ptr(), w_uv=w_uv.data_ptr(), cache=cache.data_ptr(), out=out.data_ptr(), ldq=q.stride(0),
+                              ldo=out.stride(0), slot_stride=cache.stride(0), row_slot=row_slot.data_ptr(), row_pos=row_pos.data_ptr(), batch=B,
+                              n_head=n_head, dk=dk, dv=dv, r=r, max_seq=max_seq, n_split=n_split, scale=float(scale), dtype=_code(q),
+                              workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    C.check(lib.b200_latent_decode(ctypes.byref(args), C.stream_ptr(q.device)), "latent_decode")
+    return out
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_group: int, keep: int):
+    """-> (ids int32 (n, top), weights fp32 (n, top)); see b200_moe_route."""
+    C.require_cuda(x, w_router, correction)
+    n, d = x.shape
+    E = w_router.shape[0]
+    ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    C.check(C.load_core().b200_moe_route(x.data_ptr(), w_router.data_ptr(), C.ptr(correction), ids.data_ptr(), wts.data_ptr(), n, d, E, top, n_group,
+                                         keep, _code(x), C.stream_ptr(x.device)), "moe_route")
+    return ids, wts
+
+
+MOE_GEMV_MAX_PAIRS = 64   # up to this many (token, choice) pairs the experts run as weight-streaming GEMVs
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_k wts[t, k] * W_down[ids[t, k]] relu(W_up[ids[t, k]] x[t])^2 with stacked weights (E, ff, d) / (E, d, ff)."""
+    C.require_cuda(x, ids, wts, w_up, w_down)
+    n, d = x.shape
+    E, ff, top = w_up.shape[0], w_up.shape[1], ids.shape[1]
+    lib, st, code = C.load_core(), C.stream_ptr(x.device), _code(x)
+    out = torch.empty((n, d), dtype=x.dtype, device=x.device)
+    if n * top <= MOE_GEMV_MAX_PAIRS:
+        hidden = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
+        C.check(lib.b200_moe_gemv(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), hidden.data_ptr(), out.data_ptr(),
+                                  n, top, d, ff, code, st), "moe_gemv")
+        return out
+    meta = torch.empty(2 * (E + 1) + 2 * n * top, dtype=torch.int32, device=x.device)
+    expert_off, tile_off = meta[: E + 1], meta[E + 1 : 2 * (E + 1)]
+    slot_token, slot_of = meta[2 * (E + 1) : 2 * (E + 1) + n * top], meta[2 * (E + 1) + n * top :]
+    C.check(lib.b200_moe_plan(ids.data_ptr(), n, top, E, expert_off.data_ptr(), tile_off.data_ptr(), slot_token.data_ptr(), slot_of.data_ptr(), st),
+            "moe_plan")
+    hidden = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
+    C.check(lib.b200_moe_gemm(x.data_ptr(), x.stride(0), slot_token.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), ff, expert_off.data_ptr(),
+                              tile_off.data_ptr(), n * top, E, ff, d, 1, code, st), "moe_gemm(up)")
+    y = torch.empty((n * top, d), dtype=x.dtype, device=x.device)
+    C.check(lib.b200_moe_gemm(hidden.data_ptr(), ff, None, w_down.data_ptr(), y.data_ptr(), d, expert_off.data_ptr(), tile_off.data_ptr(), n * top, E,
+                              d, ff, 0, code, st), "moe_gemm(down)")
+    C.check(lib.b200_moe_combine(y.data_ptr(), slot_of.data_ptr(), wts.data_ptr(), out.data_ptr(), n, top, d, code, st), "moe_combine")
+    return out

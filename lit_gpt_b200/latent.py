@@ -1,0 +1,118 @@
+"""Latent attention and its cache.
+
+A latent-attention layer caches ONE vector of ``kv_rank`` numbers per position (the normalised down-projection of the
+layer input) instead of keys and values; per head, keys and values are up-projections of that vector, and there is no
+rotation.  Because only the latent is cached, a layer can be told to attend over the latents ANOTHER layer has cached
+(``source``), with its own up-projections, queries and output projection.
+
+Batches are ragged: a step carries the tokens of several sequences packed into one (n, d) matrix, described by a
+``RaggedBatch`` (per row: cache slot and position; per sequence: first row, length, first position).  Prefill expands the
+context's keys and values with one matrix product and runs the tiled kernel ``K.latent_prefill``; a step of single tokens
+runs ``K.latent_decode``, which absorbs the up-projections and never materialises keys or values.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import kernels as K
+from .config import LatentMixerSpec
+
+DECODE_KEYS_PER_SPLIT = 256
+DECODE_MAX_SPLITS = 32
+
+
+def decode_splits(context: int) -> int:
+    """CTAs that share one (sequence, head) of a decode step over a context of at most `context` positions."""
+    return max(1, min(DECODE_MAX_SPLITS, -(-context // DECODE_KEYS_PER_SPLIT)))
+
+
+@dataclass
+class RaggedBatch:
+    """Device-side description of one step.  n rows (tokens) of S sequences."""
+
+    row_pos: torch.Tensor            # int32 (n,)   position of each row in its sequence
+    row_slot: torch.Tensor           # int32 (n,)   cache slot of each row
+    cache_rows: torch.Tensor         # int64 (n,)   slot * max_seq + position: where the row's latent is stored
+    decode: bool                     # every sequence brings exactly one row
+    context_hint: int                # upper bound of any row's position + 1 (sizes the decode split)
+    seqs: Optional[torch.Tensor] = None        # int32 (S, 4): first row, rows, first position, first row of its context in ctx_rows
+    ctx_rows: Optional[torch.Tensor] = None    # int64 (m,)   cache rows of every sequence's whole context, sequence after sequence
+    max_q_len: int = 1
+    identity_ctx: bool = False       # every sequence starts at position 0: the context rows ARE the step's rows, in order
+
+
+class LatentCache(nn.Module):
+    """(slots, max_seq, kv_rank) latents of one layer; slot = one live sequence."""
+
+    def __init__(self, slots: int, max_seq: int, kv_rank: int, device=None, dtype=None) -> None:
+        super().__init__()
+        self.register_buffer("latents", torch.zeros((slots, max_seq, kv_rank), device=device, dtype=dtype), persistent=False)
+
+    @property
+    def rows(self) -> torch.Tensor:
+        return self.latents.view(-1, self.latents.shape[-1])
+
+    def reset_parameters(self) -> None:
+        torch.nn.init.zeros_(self.latents)
+
+
+class LatentAttention(nn.Module):
+    def __init__(self, width: int, spec: LatentMixerSpec, eps: float, source: Optional["LatentAttention"] = None) -> None:
+        super().__init__()
+        self.spec, self.eps, self.width = spec, eps, width
+        self.owns_latent = source is None
+        self.__dict__["source"] = source if source is not None else self     # not a submodule: the owner registers its own cache
+        H = spec.heads
+        down_rows = spec.q_rank + (spec.kv_rank if self.owns_latent else 0)
+        # fused down-projection: rows [0, q_rank) give the query latent, the rest (if any) the key-value latent
+        self.w_down = nn.Parameter(torch.empty(down_rows, width), requires_grad=False)
+        self.q_norm = nn.Parameter(torch.ones(spec.q_rank), requires_grad=False)
+        self.kv_norm = nn.Parameter(torch.ones(spec.kv_rank), requires_grad=False) if self.owns_latent else None
+        self.w_uq = nn.Parameter(torch.empty(H * spec.dim, spec.q_rank), requires_grad=False)
+        # fused up-projection: rows [0, H * dim) keys, then H * vdim values
+        self.w_ukv = nn.Parameter(torch.empty(H * (spec.dim + spec.vdim), spec.kv_rank), requires_grad=False)
+        self.w_o = nn.Parameter(torch.empty(width, H * spec.vdim), requires_grad=False)
+        self.cache: Optional[LatentCache] = None
+
+    def build_cache(self, slots: int, max_seq: int, device=None, dtype=None) -> Optional[LatentCache]:
+        return LatentCache(slots, max_seq, self.spec.kv_rank, device, dtype) if self.owns_latent else None
+
+    @property
+    def w_uk(self) -> torch.Tensor:
+        return self.w_ukv[: self.spec.heads * self.spec.dim]
+
+    @property
+    def w_uv(self) -> torch.Tensor:
+        return self.w_ukv[self.spec.heads * self.spec.dim :]
+
+    def forward(self, h: torch.Tensor, batch: RaggedBatch, shared: Dict[int, torch.Tensor]) -> torch.Tensor:
+        """h (n, width) in the matrix-product dtype -> (n, width).  `shared`: per-step scratch in which the owner of a latent
+        leaves the gathered context for the layers that read it."""
+        s, n = self.spec, h.shape[0]
+        H = s.heads
+        cache = self.source.cache
+        if cache is None:
+            raise TypeError("You need to call `set_kv_cache()` first")
+        down = F.linear(h, self.w_down)
+        cq = torch.empty((n, s.q_rank), dtype=h.dtype, device=h.device)
+        segs = [K.rms_seg(down[:, : s.q_rank], self.q_norm, cq, s.q_rank, False)]
+        if self.owns_latent:   # the second half goes, normalised, straight into its cache rows
+            segs.append(K.rms_seg(down[:, s.q_rank :], self.kv_norm, cache.rows, s.kv_rank, False, out_rows=batch.cache_rows))
+        K.rms_rows(n, self.eps, *segs, in_dtype=h.dtype, out_dtype=h.dtype, device=h.device)
+        q = F.linear(cq, self.w_uq)
+        if batch.decode:
+            y = K.latent_decode(q, self.w_uk, self.w_uv, cache.latents, batch.row_slot, batch.row_pos, H, s.dim, s.vdim, s.scale,
+                                decode_splits(batch.context_hint))
+        else:
+            key = id(self.source)
+            ctx = shared.get(key)
+            if ctx is None:
+                ctx = shared[key] = K.gather_rows(cache.rows, batch.ctx_rows)
+            kv = F.linear(ctx, self.w_ukv)
+            y = K.latent_prefill(q, kv[:, : H * s.dim], kv[:, H * s.dim :], batch.seqs, batch.max_q_len, H, s.dim, s.vdim, s.scale)
+        return F.linear(y, self.w_o)

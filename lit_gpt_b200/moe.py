@@ -1,0 +1,40 @@
+"""Sparse mixture of experts with a sigmoid router.
+
+``GroupLimitedRouter``: scores s = sigmoid(W x) in fp32.  Experts are CHOSEN by s + correction (a per-expert selection bias
+that does not enter the output), among the experts of the ``keep`` best of ``groups`` equal groups of neighbouring experts --
+a group is ranked by the sum of its two largest corrected scores -- and the chosen experts are WEIGHTED by s itself, without
+renormalisation.  ``SparseExperts``: out = sum_k weight_k * W_down[e_k] relu(W_up[e_k] x)^2 over stacked expert weights, as a
+grouped matrix product for many tokens and as weight-streaming GEMVs for a few (``K.moe_experts``).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import kernels as K
+from .config import MoESpec
+
+
+class GroupLimitedRouter(nn.Module):
+    def __init__(self, width: int, experts: int, top: int, groups: int = 1, keep: int = 1) -> None:
+        super().__init__()
+        self.top, self.groups, self.keep = top, groups, keep
+        self.weight = nn.Parameter(torch.empty(experts, width), requires_grad=False)
+        self.correction = nn.Parameter(torch.zeros(experts), requires_grad=False)
+
+    def forward(self, x: torch.Tensor):
+        """x (n, width) -> (expert ids int32 (n, top), weights fp32 (n, top))"""
+        return K.moe_route(x, self.weight, self.correction, self.top, self.groups, self.keep)
+
+
+class SparseExperts(nn.Module):
+    def __init__(self, width: int, spec: MoESpec) -> None:
+        super().__init__()
+        self.spec = spec
+        self.router = GroupLimitedRouter(width, spec.experts, spec.top, spec.groups, spec.keep)
+        self.w_up = nn.Parameter(torch.empty(spec.experts, spec.ff, width), requires_grad=False)
+        self.w_down = nn.Parameter(torch.empty(spec.experts, width, spec.ff), requires_grad=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        ids, weights = self.router(x)
+        return K.moe_experts(x, ids, weights, self.w_up, self.w_down)
