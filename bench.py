@@ -459,6 +459,157 @@ def run_ours(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --compare pomipel: the Pomipel design beside the closest existing model (a Llama-shaped GPT in unquantized bf16) at equal
+# width, heads, head size, layers and feed-forward FLOPs per token; random weights.  Prints one JSON line of its own kind.
+# ---------------------------------------------------------------------------------------------------------
+ARCH_SIZES = {
+    # name: width, heads, head size, kv_rank, q_rank, experts, top, expert ff
+    "w1024": (1024, 8, 128, 256, 512, 16, 4, 512),
+    "w2048": (2048, 16, 128, 512, 1024, 32, 4, 1024),
+    "w4096": (4096, 32, 128, 512, 1536, 64, 6, 1024),
+}
+
+
+def _timed(fn, iters: int, flush) -> float:
+    """Mean device time of fn() in ms over `iters` calls, L2 flushed (a write larger than L2) before each timed call."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush.add_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def _graphed(step):
+    """step() captured in a CUDA graph (after two warm-up runs); falls back to the eager callable."""
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(); step()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        return g.replay, True
+    except Exception:
+        torch.cuda.synchronize()
+        return step, False
+
+
+def run_arch_compare(args) -> None:
+    from lit_gpt_b200 import GPT, Config
+    from lit_gpt_b200 import kernels as K
+    from lit_gpt_b200.config import LatentMixerSpec, LayerSpec, MoESpec, PomipelConfig
+    from lit_gpt_b200.pomipel import Pomipel
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, peak_source = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    n_layer, vocab, T, ctx = 4, 32000, args.prompt, args.prompt
+    iters = max(3, min(args.steps, 20))
+    launches0 = K.launch_count()
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else ARCH_SIZES):
+        d, H, hs, r, qr, E, top, ff = ARCH_SIZES[name]
+        inter = (2 * top * ff // 3 + 63) // 64 * 64     # three matrices against two: equal feed-forward FLOPs per token
+        layers = [LayerSpec("latent_attention", LatentMixerSpec(H, hs, hs, r, qr, hs ** -0.5, None if i % 2 == 0 else i - 1),
+                            MoESpec(E, top, ff, 4, 2)) for i in range(n_layer)]
+        pom = Pomipel(PomipelConfig(vocab_size=vocab, n_embd=d, block_size=ctx + 64, embedding_scale=d ** 0.5, logit_scale=1.0, layers=layers))
+        pom = pom.to(dev).to(torch.bfloat16).eval()
+        pom.reset_parameters()
+        gpt = GPT(Config(name="bench", block_size=ctx + 64, vocab_size=vocab, padding_multiple=64, n_layer=n_layer, n_head=H, n_embd=d,
+                         rotary_percentage=1.0, parallel_residual=False, bias=False, _norm_class="RMSNorm", _mlp_class="LLaMAMLP",
+                         intermediate_size=inter))
+        gpt.apply(gpt._init_weights)
+        gpt = gpt.to(dev).to(torch.bfloat16).eval()
+        res = {"gpt_intermediate": inter}
+        with torch.inference_mode():
+            for label, model in (("pomipel", pom), ("gpt", gpt)):
+                for B in (1, 8):
+                    if label == "gpt":
+                        model.set_kv_cache(batch_size=B, device=dev, dtype=torch.bfloat16)
+                    else:
+                        model.set_kv_cache(batch_size=B)
+                    idx = torch.randint(0, vocab, (B, T), device=dev)
+                    pos = torch.arange(T, device=dev)
+                    if B == 1:
+                        ms = _timed(lambda: model(idx, pos), iters, flush)
+                        res[f"{label}_prefill_tok_s"] = round(T / ms * 1e3)
+                    else:
+                        model(idx, pos)
+                    tok, p1 = idx[:, :1].contiguous(), torch.tensor([T], device=dev)
+                    step, graphed = _graphed(lambda: model(tok, p1))
+                    ms = _timed(step, iters, flush)
+                    res[f"{label}_decode_b{B}_tok_s"] = round(B / ms * 1e3)
+                    res[f"{label}_decode_b{B}_graphed"] = graphed
+                    del step
+                model.clear_kv_cache()
+            # like kernels alone, with their algorithmic work against the measured peaks
+            kern = {}
+            q = torch.randn(T, H * hs, device=dev, dtype=torch.bfloat16)
+            kv = torch.randn(T, 2 * H * hs, device=dev, dtype=torch.bfloat16)
+            seqs = torch.tensor([[0, T, 0, 0]], dtype=torch.int32, device=dev)
+            att_flops = 4.0 * H * hs * T * (T + 1) / 2
+            ms = _timed(lambda: K.latent_prefill(q, kv[:, : H * hs], kv[:, H * hs :], seqs, T, H, hs, hs, hs ** -0.5), iters, flush)
+            kern["prefill_attention_pomipel"] = {"ms": ms, "frac_of_measured_bf16": att_flops / (ms * 1e-3) / tf}
+            q4 = torch.randn(1, H, T, hs, device=dev, dtype=torch.bfloat16)
+            kc = torch.randn(1, H, T, hs, device=dev, dtype=torch.bfloat16)
+            vc = torch.randn(1, H, T, hs, device=dev, dtype=torch.bfloat16)
+            pos = torch.arange(T, device=dev)
+            ms = _timed(lambda: K.attn_prefill(q4, kc, vc, pos), iters, flush)
+            kern["prefill_attention_gpt"] = {"ms": ms, "frac_of_measured_bf16": att_flops / (ms * 1e-3) / tf}
+            B = 8
+            mx = pom.blocks[0].mixer
+            cache = torch.randn(B, ctx, r, device=dev, dtype=torch.bfloat16)
+            qd = torch.randn(B, H * hs, device=dev, dtype=torch.bfloat16)
+            slot = torch.arange(B, dtype=torch.int32, device=dev)
+            rp = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+            from lit_gpt_b200.latent import decode_splits
+            ms = _timed(lambda: K.latent_decode(qd, mx.w_uk, mx.w_uv, cache, slot, rp, H, hs, hs, hs ** -0.5, decode_splits(ctx)), iters, flush)
+            roof = max(B * ctx * r * 2 / hbm, 4.0 * B * H * ctx * r / tf)
+            kern["decode_attention_pomipel"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3),
+                                                "bytes": B * ctx * r * 2, "flops": 4.0 * B * H * ctx * r}
+            kc8 = torch.randn(B, H, ctx, hs, device=dev, dtype=torch.bfloat16)
+            vc8 = torch.randn(B, H, ctx, hs, device=dev, dtype=torch.bfloat16)
+            qkv = torch.randn(B, 3 * H * hs, device=dev, dtype=torch.bfloat16)
+            p1 = torch.tensor([ctx - 1], device=dev)
+            ms = _timed(lambda: K.attn_decode(qkv, gpt.cos, gpt.sin, p1, kc8, vc8, H, H, hs, hs), iters, flush)
+            roof = 2.0 * B * H * ctx * hs * 2 / hbm
+            kern["decode_attention_gpt"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3),
+                                            "bytes": 2.0 * B * H * ctx * hs * 2}
+            x = torch.randn(T, d, device=dev, dtype=torch.bfloat16)
+            ms = _timed(lambda: pom.blocks[0].mlp(x), iters, flush)
+            kern["feed_forward_pomipel"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * top * ff * d / (ms * 1e-3) / tf}
+            x3 = x.view(1, T, d)
+            ms = _timed(lambda: gpt.transformer.h[0].mlp(x3), iters, flush)
+            kern["feed_forward_gpt"] = {"ms": ms, "frac_of_measured_bf16": 6.0 * T * inter * d / (ms * 1e-3) / tf}
+            xs, act, w0 = torch.randn(T, d, device=dev), torch.empty(T, d, device=dev, dtype=torch.bfloat16), pom.blocks[0].norm_1
+            ms = _timed(lambda: K.residual_norm_add(x, w0, 1e-5, xs, act), iters, flush)
+            kern["residual_norm_pomipel"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            so = torch.empty_like(x)
+            ms = _timed(lambda: K.rmsnorm(x, gpt.transformer.h[0].norm_1.weight, 1e-5, delta=x, sum_out=so), iters, flush)
+            kern["residual_norm_gpt"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 2 + 2 + 2) / (ms * 1e-3) / hbm}
+            res["kernels"] = {k: {a: (round(b, 4) if isinstance(b, float) else b) for a, b in v.items()} for k, v in kern.items()}
+        out[name] = res
+        del pom, gpt
+        torch.cuda.empty_cache()
+    print(json.dumps({"compare": "pomipel", "layers": n_layer, "prompt": T, "context": ctx, "dtype": "bf16", "data": "synthetic, random weights",
+                      "l2": "flushed between timed calls", "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                                                                       "source": peak_source},
+                      "gpu_launches": int(K.launch_count() - launches0), "sizes": out}), flush=True)
+
+
 def main() -> None:
     # stdout carries exactly one JSON line: NCCL's own banner / debug lines (when the box sets NCCL_DEBUG) go to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
@@ -472,7 +623,14 @@ def main() -> None:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama2-7b-nf4-bs1")
     ap.add_argument("--layers", type=int, default=None, help="debug only: build fewer blocks (invalidates the number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--compare", choices=["pomipel"], default=None,
+                    help="instead of the default workload: prefill / decode throughput of that design beside the closest existing model")
+    ap.add_argument("--sizes", default=None, help=f"--compare: comma-separated subset of {sorted(ARCH_SIZES)}")
+    ap.add_argument("--prompt", type=int, default=2048, help="--compare: prompt and context length")
     args = ap.parse_args()
+    if args.compare:
+        run_arch_compare(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -382,7 +382,10 @@ int b200_rms_rows(const b200_rms_rows_seg* segs, int n_segs, int64_t rows, float
 /* x[row] += y[row] / sqrt(mean(y[row]^2) + eps) * (1 + weight); act[row] = dtype(x[row]) */
 int b200_residual_norm_add(const void* y, const void* weight, float eps, float* x, void* act, int64_t rows, int d, int dtype,
                            b200_stream_t stream);
-int b200_gather_rows(const void* src, const int64_t* rows, void* dst, int64_t n_rows, int d, int dtype, b200_stream_t stream);
+/* dst[i] = src[rows[i]]; rows int64 or int32 */
+int b200_gather_rows(const void* src, const void* rows, int rows_is_int64, void* dst, int64_t n_rows, int d, int dtype, b200_stream_t stream);
+/* x = relu(x)^2 in place over n elements */
+int b200_sqrelu(void* x, int64_t n, int dtype, b200_stream_t stream);
 int b200_scale_f32(const void* in, float scale, float* out, int64_t n, int dtype, b200_stream_t stream);
 
 /* Ragged causal attention with separate query-key (dk) and value (dv) sizes and no rotation.  seqs[s] = {first query row,
@@ -398,6 +401,10 @@ typedef struct b200_latent_prefill_args {
   int dtype;
 } b200_latent_prefill_args;
 int b200_latent_prefill(const b200_latent_prefill_args* args, b200_stream_t stream);
+/* The same attention on the tensor cores for bf16 operands with dk = dv = head_size in {64, 128} (the kernel of b200_attn_prefill
+ * over packed operands): leading dimensions multiples of 8 elements, q / k / v / seqs 16-byte aligned. */
+int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
+                             int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int head_size, float scale, b200_stream_t stream);
 /* One query row per sequence over cached latents (slots, max_seq, r): sequence b reads positions 0 .. row_pos[b] of slot
  * row_slot[b] (its own latent already stored).  w_uk (n_head * dk, r) and w_uv (n_head * dv, r) are absorbed: no keys or
  * values are materialised.  n_split CTAs share each (sequence, head); the workspace holds their partial results. */

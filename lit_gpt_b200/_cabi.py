@@ -95,14 +95,17 @@ class LatentDecodeArgs(ctypes.Structure):  # mirrors b200_latent_decode_args
 
 # Entry points of the sources every model needs (library state, norms, sampling) and of the fp32-residual / latent-attention /
 # expert kernels: `load_core()` can serve them from a library built from those sources alone.
-_CORE_SOURCES = ("api.cu", "norm.cu", "sample.cu", "resid.cu", "latent.cu", "moe.cu")
+_CORE_SOURCES = ("api.cu", "norm.cu", "sample.cu", "resid.cu", "latent.cu", "moe.cu", "attn_prefill.cu")
 _CORE_SIGNATURES = {
     "b200_embed_pos": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_rms_rows": (c_int, [ctypes.POINTER(RmsRowsSeg), c_int, c_int64, c_float, c_int, c_int, c_void_p]),
     "b200_residual_norm_add": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
-    "b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "b200_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "b200_sqrelu": (c_int, [c_void_p, c_int64, c_int, c_void_p]),
     "b200_scale_f32": (c_int, [c_void_p, c_float, c_void_p, c_int64, c_int, c_void_p]),
     "b200_latent_prefill": (c_int, [ctypes.POINTER(LatentPrefillArgs), c_void_p]),
+    "b200_attn_prefill_ragged": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int,
+                                         c_float, c_void_p]),
     "b200_latent_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200_latent_decode": (c_int, [ctypes.POINTER(LatentDecodeArgs), c_void_p]),
     "b200_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
@@ -113,7 +116,7 @@ _CORE_SIGNATURES = {
     "b200_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
 }
 _CORE_SHARED = ("b200_abi_version", "b200_last_error", "b200_device_info", "b200_set_pdl", "b200_launch_count", "b200_rmsnorm", "b200_swiglu",
-                "b200_embedding", "b200_argmax", "b200_sample")
+                "b200_embedding", "b200_argmax", "b200_sample", "b200_attn_prefill")
 
 _SIGNATURES = {
     "b200_abi_version": (c_int, []),

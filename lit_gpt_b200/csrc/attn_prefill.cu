@@ -21,11 +21,22 @@ constexpr int kPfBM = 128;   // query rows per CTA
 constexpr int kPfBN = 64;    // keys per tile
 constexpr int kPfThreads = 256;
 
+// Where the operands live, in elements.  The cached layout of the GQA models is (B, H or G, rows, HS); a ragged batch packs the
+// query rows of all sequences into one (rows, H * HS) matrix and gives, per sequence, seqs[b] = {first query row, query rows,
+// position of the first query row, row of position 0 in k / v} -- the positions are then pos0 + row and no pos array is read.
+struct PfView {
+  int64_t q_b, q_h, q_r;
+  int64_t k_b, k_h, k_r;
+  int64_t v_b, v_h, v_r;
+  int64_t y_b, y_r;
+  const int4* seqs;
+};
+
 template <int HS, typename PosT>
 __global__ void __launch_bounds__(kPfThreads, 1)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                     const PosT* __restrict__ pos, __nv_bfloat16* __restrict__ y, int T, int n_head, int n_groups, int max_seq,
-                    float scale_log2) {
+                    float scale_log2, PfView vw) {
   extern __shared__ __align__(128) uint8_t pf_smem_raw[];
   constexpr int CH = HS / 8;                         // 16-byte chunks per row
   constexpr int QB = kPfBM * HS * 2, KB = kPfBN * HS * 2;
@@ -41,16 +52,27 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int r0 = mt * kPfBM;
   griddep_launch();
   griddep_wait();
+  int pos0 = 0;
+  int64_t qrow0 = 0, kvrow0 = 0;
+  if (vw.seqs) {   // ragged: this sequence's own length, first position and places in the packed operands
+    const int4 sq = vw.seqs[b];
+    T = sq.y;
+    pos0 = sq.z;
+    max_seq = sq.z + sq.y;
+    qrow0 = sq.x;
+    kvrow0 = sq.w;
+    if (r0 >= T) return;
+  }
 
-  const __nv_bfloat16* qh = q + ((int64_t)b * n_head + h) * (int64_t)T * HS;
-  const __nv_bfloat16* kg = kc + ((int64_t)b * n_groups + grp) * (int64_t)max_seq * HS;
-  const __nv_bfloat16* vg = vc + ((int64_t)b * n_groups + grp) * (int64_t)max_seq * HS;
+  const __nv_bfloat16* qh = q + (int64_t)b * vw.q_b + (int64_t)h * vw.q_h + qrow0 * vw.q_r;
+  const __nv_bfloat16* kg = kc + (int64_t)b * vw.k_b + (int64_t)grp * vw.k_h + kvrow0 * vw.k_r;
+  const __nv_bfloat16* vg = vc + (int64_t)b * vw.v_b + (int64_t)grp * vw.v_h + kvrow0 * vw.v_r;
 
   // this thread's two query rows and their causal limits; the CTA's key range is [0, max limit]
   const int rowA = r0 + warp * 16 + g, rowB = rowA + 8;
   auto clampp = [&](int r) -> int {
     if (r >= T) return -1;
-    int64_t v = (int64_t)pos[r];
+    int64_t v = vw.seqs ? (int64_t)pos0 + r : (int64_t)pos[r];
     return (int)(v < 0 ? 0 : (v >= max_seq ? max_seq - 1 : v));
   };
   const int limA = clampp(rowA), limB = clampp(rowB);
@@ -63,7 +85,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   for (int i = tid; i < kPfBM * CH; i += kPfThreads) {
     const int r = i / CH, c = i % CH;
     const bool ok = r0 + r < T;
-    pf_cp16(pf_smem(sQ) + sw<HS>(r, c), qh + (int64_t)(ok ? r0 + r : 0) * HS + c * 8, ok);
+    pf_cp16(pf_smem(sQ) + sw<HS>(r, c), qh + (int64_t)(ok ? r0 + r : 0) * vw.q_r + c * 8, ok);
   }
   pf_commit();
   __syncthreads();
@@ -77,9 +99,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int i = tid; i < kPfBN * CH; i += kPfThreads) {
       const int r = i / CH, c = i % CH;
       const bool ok = j0 + r <= cta_lim;
-      const int64_t off = (int64_t)(ok ? j0 + r : 0) * HS + c * 8;
-      pf_cp16(pf_smem(sK) + buf * KB + sw<HS>(r, c), kg + off, ok);
-      pf_cp16(pf_smem(sV) + buf * KB + sw<HS>(r, c), vg + off, ok);
+      const int64_t row = ok ? j0 + r : 0;
+      pf_cp16(pf_smem(sK) + buf * KB + sw<HS>(r, c), kg + row * vw.k_r + c * 8, ok);
+      pf_cp16(pf_smem(sV) + buf * KB + sw<HS>(r, c), vg + row * vw.v_r + c * 8, ok);
     }
     pf_commit();
   };
@@ -171,14 +193,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
   lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
   const float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
-  const int64_t ystride = (int64_t)n_head * HS;
   if (rowA < T) {
-    __nv_bfloat16* yr = y + ((int64_t)b * T + rowA) * ystride + (int64_t)h * HS;
+    __nv_bfloat16* yr = y + (int64_t)b * vw.y_b + (qrow0 + rowA) * vw.y_r + (int64_t)h * HS;
 #pragma unroll
     for (int i = 0; i < HS / 8; ++i) *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(o_acc[i][0] * iA, o_acc[i][1] * iA);
   }
   if (rowB < T) {
-    __nv_bfloat16* yr = y + ((int64_t)b * T + rowB) * ystride + (int64_t)h * HS;
+    __nv_bfloat16* yr = y + (int64_t)b * vw.y_b + (qrow0 + rowB) * vw.y_r + (int64_t)h * HS;
 #pragma unroll
     for (int i = 0; i < HS / 8; ++i) *reinterpret_cast<uint32_t*>(yr + i * 8 + 2 * tq) = pack_bf16(o_acc[i][2] * iB, o_acc[i][3] * iB);
   }
@@ -186,7 +207,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
 template <int HS, typename PosT>
 cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const void* pos, void* y, int B, int T, int H, int G, int max_seq,
-                           float scale, cudaStream_t st) {
+                           float scale, cudaStream_t st, const PfView* view = nullptr) {
+  // default: q (B, H, T, HS), caches (B, G, max_seq, HS), y (B, T, H * HS)
+  const PfView vw = view ? *view
+                         : PfView{(int64_t)H * T * HS, (int64_t)T * HS, HS, (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS,
+                                  (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr};
   const size_t smem = (size_t)(kPfBM + 4 * kPfBN) * HS * 2;
   static PerDeviceOnce once;
   if (once.need()) {
@@ -196,7 +221,7 @@ cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const 
   }
   dim3 grid((T + kPfBM - 1) / kPfBM, H, B);
   return launch(attn_prefill_kernel<HS, PosT>, grid, dim3(kPfThreads), smem, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
-                (const __nv_bfloat16*)vc, (const PosT*)pos, (__nv_bfloat16*)y, T, H, G, max_seq, scale * 1.4426950408889634f);
+                (const __nv_bfloat16*)vc, (const PosT*)pos, (__nv_bfloat16*)y, T, H, G, max_seq, scale * 1.4426950408889634f, vw);
 }
 
 }  // namespace
@@ -220,5 +245,23 @@ extern "C" int b200_attn_prefill(const void* q, const void* k_cache, const void*
     if (pos_is_int64) B200_CUDA((launch_prefill<64, int64_t>(q, k_cache, v_cache, pos, y, batch, T, n_head, n_groups, max_seq, scale, st)));
     else B200_CUDA((launch_prefill<64, int32_t>(q, k_cache, v_cache, pos, y, batch, T, n_head, n_groups, max_seq, scale, st)));
   }
+  return B200_OK;
+}
+
+// Ragged batch without rotation or cache layout: packed q (rows, H * hs), k and v (context rows, H * hs) each with its own leading
+// dimension (they may be column slices of one buffer), seqs[n_seqs][4] as in PfView, y (rows, H * hs).  One head per key-value head.
+extern "C" int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
+                                        int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int head_size, float scale,
+                                        b200_stream_t stream) {
+  B200_CHECK_ARG(q && k && v && seqs && y, "b200_attn_prefill_ragged: null pointer");
+  B200_CHECK_ARG(n_seqs > 0 && n_seqs <= 65535 && max_q_len > 0 && n_head > 0 && n_head <= 65535, "b200_attn_prefill_ragged: bad shape");
+  B200_CHECK_ARG(head_size == 64 || head_size == 128, "b200_attn_prefill_ragged: head_size must be 64 or 128 (got %d)", head_size);
+  B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0, "b200_attn_prefill_ragged: leading dimensions must be multiples of 8 elements");
+  B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_ragged: operands must be 16-byte aligned");
+  const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs)};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
+  else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   return B200_OK;
 }

@@ -107,13 +107,24 @@ __global__ void __launch_bounds__(kRowThreads) residual_norm_add_kernel(const T*
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(const T* __restrict__ src, const int64_t* __restrict__ rows,
+template <typename T, typename I>
+__global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(const T* __restrict__ src, const I* __restrict__ rows,
                                                                    T* __restrict__ dst, int d) {
   griddep_launch();
   griddep_wait();
-  const int64_t r = rows[blockIdx.x];
+  const int64_t r = (int64_t)rows[blockIdx.x];
   for (int i = threadIdx.x; i < d; i += kRowThreads) dst[(int64_t)blockIdx.x * d + i] = src[r * d + i];
+}
+
+// x = relu(x)^2 in place
+template <typename T>
+__global__ void __launch_bounds__(256) sqrelu_kernel(T* __restrict__ x, int64_t n) {
+  griddep_launch();
+  griddep_wait();
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const float v = fmaxf(load_as_float(x, i), 0.f);
+    store_from_float(x, i, v * v);
+  }
 }
 
 template <typename T>
@@ -167,10 +178,23 @@ int b200_residual_norm_add(const void* y, const void* weight, float eps, float* 
   return B200_OK;
 }
 
-int b200_gather_rows(const void* src, const int64_t* rows, void* dst, int64_t n_rows, int d, int dtype, b200_stream_t stream) {
+int b200_gather_rows(const void* src, const void* rows, int rows_is_int64, void* dst, int64_t n_rows, int d, int dtype, b200_stream_t stream) {
   B200_CHECK_ARG(src && rows && dst && n_rows > 0 && n_rows <= 0x7fffffff && d > 0, "b200_gather_rows: bad argument");
-  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(gather_rows_kernel<T>, dim3((unsigned)n_rows), dim3(kRowThreads), 0, (cudaStream_t)stream,
-                                               (const T*)src, rows, (T*)dst, d)));
+  if (rows_is_int64)
+    B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(gather_rows_kernel<T, int64_t>, dim3((unsigned)n_rows), dim3(kRowThreads), 0, (cudaStream_t)stream,
+                                                 (const T*)src, (const int64_t*)rows, (T*)dst, d)));
+  else
+    B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(gather_rows_kernel<T, int32_t>, dim3((unsigned)n_rows), dim3(kRowThreads), 0, (cudaStream_t)stream,
+                                                 (const T*)src, (const int32_t*)rows, (T*)dst, d)));
+  return B200_OK;
+}
+
+int b200_sqrelu(void* x, int64_t n, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(x && n > 0, "b200_sqrelu: bad argument");
+  int64_t blocks = (n + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(sqrelu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (T*)x, n)));
   return B200_OK;
 }
 

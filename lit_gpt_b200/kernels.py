@@ -632,13 +632,22 @@ def residual_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, x: torc
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     C.require_cuda(src, rows)
-    if not src.is_contiguous() or rows.dtype != torch.int64:
-        raise C.B200Error("gather_rows: contiguous source and int64 rows")
+    if not src.is_contiguous() or rows.dtype not in (torch.int64, torch.int32) or not rows.is_contiguous():
+        raise C.B200Error("gather_rows: contiguous source and int64 / int32 rows")
     d = src.shape[-1]
     dst = torch.empty((rows.numel(), d), dtype=src.dtype, device=src.device)
-    C.check(C.load_core().b200_gather_rows(src.data_ptr(), rows.data_ptr(), dst.data_ptr(), rows.numel(), d, _code(src), C.stream_ptr(src.device)),
-            "gather_rows")
+    C.check(C.load_core().b200_gather_rows(src.data_ptr(), rows.data_ptr(), int(rows.dtype == torch.int64), dst.data_ptr(), rows.numel(), d, _code(src),
+                                           C.stream_ptr(src.device)), "gather_rows")
     return dst
+
+
+def sqrelu_(x: torch.Tensor) -> torch.Tensor:
+    """x = relu(x)^2 in place."""
+    C.require_cuda(x)
+    if not x.is_contiguous():
+        raise C.B200Error("sqrelu_: contiguous tensor")
+    C.check(C.load_core().b200_sqrelu(x.data_ptr(), x.numel(), _code(x), C.stream_ptr(x.device)), "sqrelu")
+    return x
 
 
 def scale_f32(t: torch.Tensor, scale: float) -> torch.Tensor:
@@ -647,6 +656,9 @@ def scale_f32(t: torch.Tensor, scale: float) -> torch.Tensor:
     out = torch.empty(t.shape, dtype=torch.float32, device=t.device)
     C.check(C.load_core().b200_scale_f32(t.data_ptr(), float(scale), out.data_ptr(), t.numel(), _code(t), C.stream_ptr(t.device)), "scale_f32")
     return out
+
+
+LATENT_PREFILL_MMA = True   # tests switch it off to reach the any-size kernel with tensor-core-sized heads
 
 
 def latent_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqs: torch.Tensor, max_q_len: int, n_head: int, dk: int, dv: int,
@@ -659,6 +671,13 @@ def latent_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqs: torc
     if not (q.dtype == k.dtype == v.dtype) or q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1:
         raise C.B200Error("latent_prefill: q, k, v of one dtype with unit inner stride")
     out = torch.empty((q.shape[0], n_head * dv), dtype=q.dtype, device=q.device)
+    if (q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128) and not (q.stride(0) | k.stride(0) | v.stride(0)) & 7
+            and not (q.data_ptr() | k.data_ptr() | v.data_ptr() | seqs.data_ptr()) & 15 and LATENT_PREFILL_MMA):
+        # tensor-core tiles of the GQA models' prefill kernel, over the packed operands
+        C.check(C.load_core().b200_attn_prefill_ragged(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), seqs.data_ptr(),
+                                                       seqs.shape[0], max_q_len, out.data_ptr(), out.stride(0), n_head, dk, float(scale),
+                                                       C.stream_ptr(q.device)), "attn_prefill_ragged")
+        return out
     args = C.LatentPrefillArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
                                ldo=out.stride(0), seqs=seqs.data_ptr(), n_seqs=seqs.shape[0], max_q_len=max_q_len, n_head=n_head, dk=dk, dv=dv,
                                scale=float(scale), dtype=_code(q))
@@ -714,16 +733,40 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
         C.check(lib.b200_moe_gemv(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), hidden.data_ptr(), out.data_ptr(),
                                   n, top, d, ff, code, st), "moe_gemv")
         return out
-    meta = torch.empty(2 * (E + 1) + 2 * n * top, dtype=torch.int32, device=x.device)
-    expert_off, tile_off = meta[: E + 1], meta[E + 1 : 2 * (E + 1)]
-    slot_token, slot_of = meta[2 * (E + 1) : 2 * (E + 1) + n * top], meta[2 * (E + 1) + n * top :]
-    C.check(lib.b200_moe_plan(ids.data_ptr(), n, top, E, expert_off.data_ptr(), tile_off.data_ptr(), slot_token.data_ptr(), slot_of.data_ptr(), st),
-            "moe_plan")
+    plan = moe_plan(ids, E)
     hidden = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
-    C.check(lib.b200_moe_gemm(x.data_ptr(), x.stride(0), slot_token.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), ff, expert_off.data_ptr(),
-                              tile_off.data_ptr(), n * top, E, ff, d, 1, code, st), "moe_gemm(up)")
+    C.check(lib.b200_moe_gemm(x.data_ptr(), x.stride(0), plan.slot_token.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), ff, plan.expert_off.data_ptr(),
+                              plan.tile_off.data_ptr(), n * top, E, ff, d, 1, code, st), "moe_gemm(up)")
     y = torch.empty((n * top, d), dtype=x.dtype, device=x.device)
-    C.check(lib.b200_moe_gemm(hidden.data_ptr(), ff, None, w_down.data_ptr(), y.data_ptr(), d, expert_off.data_ptr(), tile_off.data_ptr(), n * top, E,
-                              d, ff, 0, code, st), "moe_gemm(down)")
-    C.check(lib.b200_moe_combine(y.data_ptr(), slot_of.data_ptr(), wts.data_ptr(), out.data_ptr(), n, top, d, code, st), "moe_combine")
+    C.check(lib.b200_moe_gemm(hidden.data_ptr(), ff, None, w_down.data_ptr(), y.data_ptr(), d, plan.expert_off.data_ptr(), plan.tile_off.data_ptr(),
+                              n * top, E, d, ff, 0, code, st), "moe_gemm(down)")
+    return moe_combine(y, plan, wts)
+
+
+class MoEPlan:
+    """The (token, choice) pairs of a step sorted by expert: rows [expert_off[e], expert_off[e + 1]) belong to expert e;
+    slot_token[row] is the token of a sorted row, slot_of[t * top + k] the row of a pair (all int32, on the device)."""
+
+    __slots__ = ("expert_off", "tile_off", "slot_token", "slot_of", "tokens", "top")
+
+
+def moe_plan(ids: torch.Tensor, n_expert: int) -> MoEPlan:
+    n, top = ids.shape
+    E = n_expert
+    meta = torch.empty(2 * (E + 1) + 2 * n * top, dtype=torch.int32, device=ids.device)
+    plan = MoEPlan()
+    plan.tokens, plan.top = n, top
+    plan.expert_off, plan.tile_off = meta[: E + 1], meta[E + 1 : 2 * (E + 1)]
+    plan.slot_token, plan.slot_of = meta[2 * (E + 1) : 2 * (E + 1) + n * top], meta[2 * (E + 1) + n * top :]
+    C.check(C.load_core().b200_moe_plan(ids.data_ptr(), n, top, E, plan.expert_off.data_ptr(), plan.tile_off.data_ptr(), plan.slot_token.data_ptr(),
+                                        plan.slot_of.data_ptr(), C.stream_ptr(ids.device)), "moe_plan")
+    return plan
+
+
+def moe_combine(y: torch.Tensor, plan: MoEPlan, wts: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_k wts[t, k] * y[slot_of[t, k]] (fp32 sum in the order of k)."""
+    d = y.shape[-1]
+    out = torch.empty((plan.tokens, d), dtype=y.dtype, device=y.device)
+    C.check(C.load_core().b200_moe_combine(y.data_ptr(), plan.slot_of.data_ptr(), wts.data_ptr(), out.data_ptr(), plan.tokens, plan.top, d, _code(y),
+                                           C.stream_ptr(y.device)), "moe_combine")
     return out

@@ -4,7 +4,8 @@
 that does not enter the output), among the experts of the ``keep`` best of ``groups`` equal groups of neighbouring experts --
 a group is ranked by the sum of its two largest corrected scores -- and the chosen experts are WEIGHTED by s itself, without
 renormalisation.  ``SparseExperts``: out = sum_k weight_k * W_down[e_k] relu(W_up[e_k] x)^2 over stacked expert weights, as a
-grouped matrix product for many tokens and as weight-streaming GEMVs for a few (``K.moe_experts``).
+grouped matrix product for many tokens (the vendor's grouped GEMM for bf16, this library's any-size fp32-accumulating kernel
+otherwise) and as weight-streaming GEMVs for a few (``K.moe_experts``).
 """
 from __future__ import annotations
 
@@ -13,6 +14,9 @@ import torch.nn as nn
 
 from . import kernels as K
 from .config import MoESpec
+
+
+VENDOR_GROUPED_GEMM = True   # tests switch it off to run the library's own grouped kernel on the same input
 
 
 class GroupLimitedRouter(nn.Module):
@@ -37,4 +41,14 @@ class SparseExperts(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ids, weights = self.router(x)
-        return K.moe_experts(x, ids, weights, self.w_up, self.w_down)
+        n, d = x.shape
+        if (n * self.spec.top <= K.MOE_GEMV_MAX_PAIRS or x.dtype != torch.bfloat16 or d % 8 or self.spec.ff % 8
+                or not VENDOR_GROUPED_GEMM or not hasattr(torch, "_grouped_mm")):
+            return K.moe_experts(x, ids, weights, self.w_up, self.w_down)   # this library's kernels only (always so in fp32)
+        # many bf16 tokens: the two products go to the vendor's grouped GEMM (as the dense products go to its GEMM), over the
+        # rows this library sorted by expert on the device -- no host round trip for the per-expert counts
+        plan = K.moe_plan(ids, self.spec.experts)
+        ends = plan.expert_off[1:]
+        hidden = torch._grouped_mm(K.gather_rows(x, plan.slot_token), self.w_up.transpose(1, 2), offs=ends)
+        y = torch._grouped_mm(K.sqrelu_(hidden), self.w_down.transpose(1, 2), offs=ends)
+        return K.moe_combine(y, plan, weights)

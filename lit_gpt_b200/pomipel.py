@@ -150,6 +150,18 @@ class Pomipel(nn.Module):
         return (self.max_seq_length, caches, self.embed.data_ptr(), self.head.data_ptr())
 
     # ---- weights ----------------------------------------------------------------------------------------------------
+    def reset_parameters(self, seed: int = 1234, std: float = 0.02) -> None:
+        """Random weights for benchmarks and smoke runs: N(0, std) matrices, unit plain norms, zero-centred norms and selection
+        biases at zero."""
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        for name, p in self.named_parameters():
+            if name.endswith(("q_norm", "kv_norm")):
+                p.data.fill_(1.0)
+            elif p.dim() == 1:
+                p.data.zero_()
+            else:
+                p.data.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0.0, std, generator=gen))
+
     def load_tensors(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Fill the parameters from the checkpoint's tensors: ``embed``, ``pos``, ``final.norm``, ``head`` and per layer i
         ``l<i>.norm1|norm2``, ``l<i>.mix.dq|dq.norm|uq|dkv|dkv.norm|uk|uv|o``, ``l<i>.mlp.router|correction|e<j>.up|e<j>.down``.

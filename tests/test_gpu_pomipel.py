@@ -234,6 +234,27 @@ def test_experts(dtype, n):
         assert rel_err(again, got) < (1e-6 if dtype == torch.float32 else 1e-2)
 
 
+def test_expert_module_vendor_grouped_path_agrees_with_own_kernels():
+    import lit_gpt_b200.moe as M
+    from lit_gpt_b200.config import MoESpec
+
+    g = torch.Generator().manual_seed(3)
+    layer = M.SparseExperts(64, MoESpec(experts=8, top=3, ff=40, groups=4, keep=2)).cuda().to(torch.bfloat16)
+    for p in layer.parameters():
+        p.data.copy_(torch.randn(p.shape, generator=g) * (0.4 if p.dim() == 1 else p.shape[-1] ** -0.5))
+    layer.router.correction.data[5] = -40.0   # an expert without tokens in the middle of the sorted rows
+    x = torch.randn(300, 64, generator=g).to(torch.bfloat16).cuda()
+    vendor = layer(x)
+    M.VENDOR_GROUPED_GEMM = False
+    try:
+        own = layer(x)
+    finally:
+        M.VENDOR_GROUPED_GEMM = True
+    assert rel_err(vendor, own) < 1e-2
+    few = layer(x[:4])     # GEMV path on the first rows
+    assert rel_err(few, own[:4]) < 1e-2
+
+
 def _attention_reference(q, kk, v, scale, start):
     """q (T, H, dk) at positions start .., kk (start + T, H, dk), v (.., H, dv), all float64"""
     T, H, _ = q.shape
@@ -246,7 +267,7 @@ def _attention_reference(q, kk, v, scale, start):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("dk,dv", [(20, 12), (64, 160), (36, 64)])
+@pytest.mark.parametrize("dk,dv", [(20, 12), (64, 160), (36, 64), (64, 64), (128, 128)])   # the last two: tensor-core kernel in bf16
 def test_prefill_attention_ragged(dtype, dk, dv):
     """Three sequences of unequal length in one launch, one of them continuing at a later position, lengths around the 64-row and
     64-key tile edges."""
@@ -268,6 +289,14 @@ def test_prefill_attention_ragged(dtype, dk, dv):
     got = k.latent_prefill(torch.cat(qs).cuda(), kv[:, : H * dk], kv[:, H * dk :], torch.tensor(meta, dtype=torch.int32, device="cuda"),
                            max(t for _, t in shapes), H, dk, dv, scale)
     assert rel_err(got, torch.cat(want)) < (2e-6 if dtype == torch.float32 else 8e-3)
+    if dtype == torch.bfloat16 and dk == dv:   # the any-size kernel on the same operands
+        k.LATENT_PREFILL_MMA = False
+        try:
+            plain = k.latent_prefill(torch.cat(qs).cuda(), kv[:, : H * dk], kv[:, H * dk :], torch.tensor(meta, dtype=torch.int32, device="cuda"),
+                                     max(t for _, t in shapes), H, dk, dv, scale)
+        finally:
+            k.LATENT_PREFILL_MMA = True
+        assert rel_err(plain, torch.cat(want)) < 8e-3
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
