@@ -419,6 +419,8 @@ typedef struct b200_latent_decode_args {
 } b200_latent_decode_args;
 size_t b200_latent_decode_workspace_bytes(int batch, int n_head, int r, int n_split);
 int b200_latent_decode(const b200_latent_decode_args* args, b200_stream_t stream);
+/* test knob: non-zero keeps bf16 decode on the any-size kernel instead of the tensor-core one; returns the previous setting */
+int b200_latent_decode_tune(int force_any_size_kernel);
 
 /* Router: s = sigmoid(W_router x); experts are chosen by s + correction among the `keep` best of `n_group` equal groups of
  * neighbours (group rank = sum of its two largest corrected scores); weights[t, k] = s of the chosen expert. */

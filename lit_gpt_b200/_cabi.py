@@ -108,6 +108,7 @@ _CORE_SIGNATURES = {
                                          c_float, c_void_p]),
     "b200_latent_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200_latent_decode": (c_int, [ctypes.POINTER(LatentDecodeArgs), c_void_p]),
+    "b200_latent_decode_tune": (c_int, [c_int]),
     "b200_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_moe_plan": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_moe_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,

@@ -9,8 +9,11 @@
 //  * decode (one query row per sequence): the up-projections are absorbed -- q'_h = W_uk[h]^T q_h (r numbers), scores are
 //    q'_h . c_j over the cached latents, the probabilities average the latents themselves, and W_uv[h] is applied once to
 //    that average.  Work per cached position is 2 r MACs per head instead of re-expanding dk + dv numbers; the context is
-//    split over CTAs (split-K) and a second kernel merges the splits and applies W_uv.
-#include "common.cuh"
+//    split over CTAs (split-K) and a last kernel merges the splits and applies W_uv.  For bf16 the split runs on the
+//    tensor cores with sixteen heads as the rows of one tile; fp32 models and odd latent sizes take the any-size kernel.
+#include <type_traits>
+
+#include "mma_tile.cuh"
 
 namespace b200 {
 
@@ -181,19 +184,36 @@ __global__ void __launch_bounds__(kLpThreads) latent_prefill_kernel(const T* __r
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kLdThreads = 128, kLdTile = 32, kLdMaxRPT = 8;   // latent size <= 128 * 8
 
+// grid (n_head, batch): q'_h = (W_uk[h]^T q_h) * scale * log2(e), r numbers in fp32 -- the query in latent space
+template <typename T>
+__global__ void __launch_bounds__(kLdThreads) latent_absorb_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ w_uk,
+                                                                    float* __restrict__ qlat, int dk, int r, float scale_log2) {
+  extern __shared__ __align__(16) float ab_smem[];   // [dk]
+  griddep_launch();
+  griddep_wait();
+  const int h = blockIdx.x, b = blockIdx.y, n_head = gridDim.x, tid = threadIdx.x;
+  for (int d = tid; d < dk; d += kLdThreads) ab_smem[d] = load_as_float(q, (int64_t)b * ldq + (int64_t)h * dk + d);
+  __syncthreads();
+  const T* w = w_uk + (int64_t)h * dk * r;
+  for (int rr = tid; rr < r; rr += kLdThreads) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < dk; ++d) acc = fmaf(ab_smem[d], load_as_float(w, (int64_t)d * r + rr), acc);
+    qlat[((int64_t)b * n_head + h) * r + rr] = acc * scale_log2;
+  }
+}
+
 // grid (n_split, n_head, batch).  Partial result of one split: r unnormalised latent sums, then the running maximum
 // (log2 domain) and the probability sum.
 template <typename T>
-__global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ w_uk,
-                                                                          const T* __restrict__ cache, int64_t slot_stride,
-                                                                          const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-                                                                          float* __restrict__ ws, int n_head, int dk, int r,
-                                                                          float scale_log2, int max_seq) {
+__global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const float* __restrict__ qlat, const T* __restrict__ cache,
+                                                                          int64_t slot_stride, const int* __restrict__ row_slot,
+                                                                          const int* __restrict__ row_pos, float* __restrict__ ws, int n_head,
+                                                                          int r, int max_seq) {
   extern __shared__ __align__(16) unsigned char ld_smem_raw[];
   griddep_launch();
   griddep_wait();
-  float* const qs = reinterpret_cast<float*>(ld_smem_raw);   // [dk]
-  float* const ql = qs + dk;                                   // [r]  q' = scale * W_uk[h]^T q
+  float* const ql = reinterpret_cast<float*>(ld_smem_raw);    // [r]  q'
   float* const sc = ql + r;                                    // [32] scores, then probabilities
   float* const st = sc + kLdTile;                              // [4]  running max, sum, rescale factor
   T* const cs = reinterpret_cast<T*>(st + 4);                  // [32][r]
@@ -206,14 +226,8 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const T
   const int k0 = split * per, k1 = min(ctx, k0 + per);
   const T* crow = cache + (int64_t)row_slot[b] * slot_stride;
 
-  for (int d = tid; d < dk; d += kLdThreads) qs[d] = load_as_float(q, (int64_t)b * ldq + (int64_t)h * dk + d);
+  for (int rr = tid; rr < r; rr += kLdThreads) ql[rr] = qlat[((int64_t)b * n_head + h) * r + rr];
   if (tid == 0) { st[0] = -INFINITY; st[1] = 0.f; st[2] = 1.f; }
-  __syncthreads();
-  for (int rr = tid; rr < r; rr += kLdThreads) {
-    float acc = 0.f;
-    for (int d = 0; d < dk; ++d) acc = fmaf(qs[d], load_as_float(w_uk, ((int64_t)h * dk + d) * r + rr), acc);
-    ql[rr] = acc * scale_log2;
-  }
   float o[kLdMaxRPT];
 #pragma unroll
   for (int i = 0; i < kLdMaxRPT; ++i) o[i] = 0.f;
@@ -266,6 +280,128 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_split_kernel(const T
     if (rr < r) dst[rr] = o[i];
   }
   if (tid == 0) { dst[r] = st[0]; dst[r + 1] = st[1]; }
+}
+
+// The same split on the tensor cores (bf16, r a multiple of 32, r <= 512): one CTA takes 16 heads of one sequence, so the
+// scores of a 32-key tile are one (16 x r) . (r x 32) product and the probability-weighted latent sum a (16 x 32) . (32 x r)
+// product, both mma.sync.m16n8k16 with fp32 accumulation; q' and the probabilities are rounded to bf16 as operands.
+// Warp w computes the scores of keys 8 w .. 8 w + 7 and owns columns [w r / 4, (w + 1) r / 4) of the latent sum.
+// grid (n_split, ceil(n_head / 16), batch); partial results in the layout of the kernel above.
+constexpr int kLmHeads = 16, kLmMaxNT = 16;
+
+__global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const float* __restrict__ qlat, const __nv_bfloat16* __restrict__ cache,
+                                                                        int64_t slot_stride, const int* __restrict__ row_slot,
+                                                                        const int* __restrict__ row_pos, float* __restrict__ ws, int n_head,
+                                                                        int r, int max_seq) {
+  extern __shared__ __align__(16) unsigned char lm_smem_raw[];
+  griddep_launch();
+  griddep_wait();
+  const int pitch = r + 8;                                              // bf16 elements; rows stay 16-byte aligned and spread over the banks
+  __nv_bfloat16* const Qs = reinterpret_cast<__nv_bfloat16*>(lm_smem_raw);   // [16][pitch]
+  __nv_bfloat16* const Cs = Qs + kLmHeads * pitch;                            // [32][pitch]
+  __nv_bfloat16* const Ps = Cs + kLdTile * pitch;                             // [16][40]
+  float* const smax = reinterpret_cast<float*>(Ps + kLmHeads * 40);          // [4][16]
+  float* const ssum = smax + 4 * kLmHeads;                                    // [4][16]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+  const int split = blockIdx.x, n_split = gridDim.x, h0 = blockIdx.y * kLmHeads, b = blockIdx.z;
+  int ctx = row_pos[b] + 1;
+  ctx = ctx < 1 ? 1 : (ctx > max_seq ? max_seq : ctx);
+  int per = (ctx + n_split - 1) / n_split;
+  per = (per + kLdTile - 1) / kLdTile * kLdTile;
+  const int k0 = split * per, k1 = min(ctx, k0 + per);
+  const __nv_bfloat16* crow = cache + (int64_t)row_slot[b] * slot_stride;
+  const int nt = r / 32;                                                 // 8-column tiles of the latent sum per warp
+  const int chunks = r / 8;                                              // 16-byte chunks per latent
+
+  for (int idx = tid; idx < kLmHeads * r; idx += kLdThreads) {
+    const int hh = idx / r, rr = idx - hh * r;
+    Qs[hh * pitch + rr] = __float2bfloat16_rn(h0 + hh < n_head ? qlat[((int64_t)b * n_head + h0 + hh) * r + rr] : 0.f);
+  }
+  float o[kLmMaxNT][4];
+#pragma unroll
+  for (int i = 0; i < kLmMaxNT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;             // rows g and g + 8, identical in every warp
+
+  for (int j0 = k0; j0 < k1; j0 += kLdTile) {
+    __syncthreads();                                                     // previous tile consumed; Qs visible on the first pass
+    const int nj = min(kLdTile, k1 - j0);
+    for (int idx = tid; idx < kLdTile * chunks; idx += kLdThreads) {
+      const int j = idx / chunks, c = idx - j * chunks;
+      pf_cp16(pf_smem(Cs + j * pitch + c * 8), crow + (int64_t)(j0 + (j < nj ? j : 0)) * r + c * 8, j < nj);
+    }
+    pf_commit();
+    pf_wait<0>();
+    __syncthreads();
+    // scores of this warp's eight keys for the sixteen heads
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int ks = 0; ks < r / 32; ++ks) {
+      uint32_t a0[4], a1[4], kb[4];
+      ldsm_x4(a0, pf_smem(Qs + (lane & 15) * pitch + ks * 32 + (lane >> 4) * 8));
+      ldsm_x4(a1, pf_smem(Qs + (lane & 15) * pitch + ks * 32 + 16 + (lane >> 4) * 8));
+      ldsm_x4(kb, pf_smem(Cs + (warp * 8 + (lane & 7)) * pitch + ks * 32 + (lane >> 3) * 8));
+      pf_mma(sacc, a0, kb[0], kb[1]);
+      pf_mma(sacc, a1, kb[2], kb[3]);
+    }
+    const int key = warp * 8 + 2 * tq;
+    if (key >= nj) sacc[0] = sacc[2] = -INFINITY;
+    if (key + 1 >= nj) sacc[1] = sacc[3] = -INFINITY;
+    float tA = fmaxf(sacc[0], sacc[1]), tB = fmaxf(sacc[2], sacc[3]);
+    tA = fmaxf(tA, __shfl_xor_sync(0xffffffffu, tA, 1)); tA = fmaxf(tA, __shfl_xor_sync(0xffffffffu, tA, 2));
+    tB = fmaxf(tB, __shfl_xor_sync(0xffffffffu, tB, 1)); tB = fmaxf(tB, __shfl_xor_sync(0xffffffffu, tB, 2));
+    if (tq == 0) { smax[warp * kLmHeads + g] = tA; smax[warp * kLmHeads + g + 8] = tB; }
+    __syncthreads();
+    float nA = mA, nB = mB;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { nA = fmaxf(nA, smax[w * kLmHeads + g]); nB = fmaxf(nB, smax[w * kLmHeads + g + 8]); }
+    const float cA = exp2f(mA - nA), cB = exp2f(mB - nB);                // the first key of a split is always visible: nA, nB finite
+    const float p0 = exp2f(sacc[0] - nA), p1 = exp2f(sacc[1] - nA), p2 = exp2f(sacc[2] - nB), p3 = exp2f(sacc[3] - nB);
+    *reinterpret_cast<uint32_t*>(Ps + g * 40 + key) = pack_bf16(p0, p1);
+    *reinterpret_cast<uint32_t*>(Ps + (g + 8) * 40 + key) = pack_bf16(p2, p3);
+    float rA = p0 + p1, rB = p2 + p3;
+    rA += __shfl_xor_sync(0xffffffffu, rA, 1); rA += __shfl_xor_sync(0xffffffffu, rA, 2);
+    rB += __shfl_xor_sync(0xffffffffu, rB, 1); rB += __shfl_xor_sync(0xffffffffu, rB, 2);
+    if (tq == 0) { ssum[warp * kLmHeads + g] = rA; ssum[warp * kLmHeads + g + 8] = rB; }
+    __syncthreads();
+    float sA = 0.f, sB = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { sA += ssum[w * kLmHeads + g]; sB += ssum[w * kLmHeads + g + 8]; }
+    lA = lA * cA + sA; lB = lB * cB + sB;
+    mA = nA; mB = nB;
+    // latent sum: this warp's columns, all 32 keys
+    uint32_t pa0[4], pa1[4];
+    ldsm_x4(pa0, pf_smem(Ps + (lane & 15) * 40 + (lane >> 4) * 8));
+    ldsm_x4(pa1, pf_smem(Ps + (lane & 15) * 40 + 16 + (lane >> 4) * 8));
+    const int col0 = warp * (r / 4);
+#pragma unroll
+    for (int i = 0; i < kLmMaxNT; i += 2) {
+      if (i < nt) {
+        o[i][0] *= cA; o[i][1] *= cA; o[i][2] *= cB; o[i][3] *= cB;
+        o[i + 1][0] *= cA; o[i + 1][1] *= cA; o[i + 1][2] *= cB; o[i + 1][3] *= cB;
+        uint32_t v0[4], v1[4];
+        const int krow = (((lane >> 3) & 1) << 3) + (lane & 7), col = col0 + i * 8 + (lane >> 4) * 8;
+        ldsm_x4_t(v0, pf_smem(Cs + krow * pitch + col));
+        ldsm_x4_t(v1, pf_smem(Cs + (16 + krow) * pitch + col));
+        pf_mma(o[i], pa0, v0[0], v0[1]);
+        pf_mma(o[i + 1], pa0, v0[2], v0[3]);
+        pf_mma(o[i], pa1, v1[0], v1[1]);
+        pf_mma(o[i + 1], pa1, v1[2], v1[3]);
+      }
+    }
+  }
+  const int col0 = warp * (r / 4);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int h = h0 + g + 8 * half;
+    if (h >= n_head) continue;
+    float* dst = ws + (((int64_t)b * n_head + h) * n_split + split) * (r + 2);
+#pragma unroll
+    for (int i = 0; i < kLmMaxNT; ++i)
+      if (i < nt) {
+        dst[col0 + i * 8 + 2 * tq] = o[i][2 * half];
+        dst[col0 + i * 8 + 2 * tq + 1] = o[i][2 * half + 1];
+      }
+    if (warp == 0 && tq == 0) { dst[r] = half ? mB : mA; dst[r + 1] = half ? lB : lA; }
+  }
 }
 
 // grid (n_head, batch): merge the splits, then out_h = W_uv[h] (sum_j p_j c_j)
@@ -324,22 +460,38 @@ int prefill_launch(const b200_latent_prefill_args* a, cudaStream_t st) {
   return B200_OK;
 }
 
+std::atomic<int> g_decode_simt{0};   // test knob: keep bf16 decode on the any-size kernel
+
 template <typename T>
 int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
-  const size_t smem1 = (size_t)(a->dk + a->r + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * a->r * sizeof(T);
+  const size_t smem0 = (size_t)a->dk * sizeof(float);
+  const size_t smem1 = (size_t)(a->r + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * a->r * sizeof(T);
   const size_t smem2 = (size_t)(a->r + a->n_split) * sizeof(float);
-  B200_CHECK_ARG(smem1 <= 227 * 1024 && smem2 <= 227 * 1024, "b200_latent_decode: sizes need too much shared memory");
+  const size_t smem3 = (size_t)((kLmHeads + kLdTile) * (a->r + 8) + kLmHeads * 40) * 2 + 8 * kLmHeads * sizeof(float);
+  B200_CHECK_ARG(smem0 <= 48 * 1024 && smem1 <= 227 * 1024 && smem2 <= 227 * 1024, "b200_latent_decode: sizes need too much shared memory");
   static PerDeviceOnce once;
   if (once.need()) {
     B200_CUDA(cudaFuncSetAttribute(latent_decode_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     B200_CUDA(cudaFuncSetAttribute(latent_decode_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(latent_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     once.done();
   }
-  B200_CUDA(launch(latent_decode_split_kernel<T>, dim3((unsigned)a->n_split, (unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem1, st,
-                   (const T*)a->q, a->ldq, (const T*)a->w_uk, (const T*)a->cache, a->slot_stride, a->row_slot, a->row_pos, (float*)a->workspace,
-                   a->n_head, a->dk, a->r, a->scale * 1.4426950408889634f, a->max_seq));
+  float* qlat = (float*)a->workspace;
+  float* parts = qlat + (size_t)a->batch * a->n_head * a->r;
+  const float scale_log2 = a->scale * 1.4426950408889634f;
+  B200_CUDA(launch(latent_absorb_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem0, st, (const T*)a->q, a->ldq,
+                   (const T*)a->w_uk, qlat, a->dk, a->r, scale_log2));
+  const bool tensor = std::is_same<T, __nv_bfloat16>::value && a->r % 32 == 0 && a->r <= 32 * kLmMaxNT && !g_decode_simt.load() &&
+                      (reinterpret_cast<uintptr_t>(a->cache) & 15) == 0 && (a->slot_stride & 7) == 0;
+  if (tensor)
+    B200_CUDA(launch(latent_decode_mma_kernel, dim3((unsigned)a->n_split, (unsigned)((a->n_head + kLmHeads - 1) / kLmHeads), (unsigned)a->batch),
+                     dim3(kLdThreads), smem3, st, (const float*)qlat, (const __nv_bfloat16*)a->cache, a->slot_stride, a->row_slot, a->row_pos, parts,
+                     a->n_head, a->r, a->max_seq));
+  else
+    B200_CUDA(launch(latent_decode_split_kernel<T>, dim3((unsigned)a->n_split, (unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem1, st,
+                     (const float*)qlat, (const T*)a->cache, a->slot_stride, a->row_slot, a->row_pos, parts, a->n_head, a->r, a->max_seq));
   B200_CUDA(launch(latent_decode_merge_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem2, st,
-                   (const float*)a->workspace, (const T*)a->w_uv, (T*)a->out, a->ldo, a->n_head, a->dv, a->r, a->n_split));
+                   (const float*)parts, (const T*)a->w_uv, (T*)a->out, a->ldo, a->n_head, a->dv, a->r, a->n_split));
   return B200_OK;
 }
 
@@ -363,8 +515,10 @@ int b200_latent_prefill(const b200_latent_prefill_args* a, b200_stream_t stream)
 }
 
 size_t b200_latent_decode_workspace_bytes(int batch, int n_head, int r, int n_split) {
-  return (size_t)batch * n_head * n_split * (r + 2) * sizeof(float);
+  return ((size_t)batch * n_head * r + (size_t)batch * n_head * n_split * (r + 2)) * sizeof(float);
 }
+
+int b200_latent_decode_tune(int force_any_size_kernel) { return b200::g_decode_simt.exchange(force_any_size_kernel ? 1 : 0); }
 
 int b200_latent_decode(const b200_latent_decode_args* a, b200_stream_t stream) {
   B200_CHECK_ARG(a && a->q && a->w_uk && a->w_uv && a->cache && a->row_slot && a->row_pos && a->out && a->workspace,

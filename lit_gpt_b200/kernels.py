@@ -706,6 +706,11 @@ def latent_decode(q: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, cache
     return out
 
 
+def latent_decode_tune(force_any_size_kernel: bool = False) -> bool:
+    """Test knob: keep bf16 decode attention on the any-size kernel; returns the previous setting."""
+    return bool(C.load_core().b200_latent_decode_tune(int(force_any_size_kernel)))
+
+
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_group: int, keep: int):
     """-> (ids int32 (n, top), weights fp32 (n, top)); see b200_moe_route."""
     C.require_cuda(x, w_router, correction)

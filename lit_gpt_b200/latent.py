@@ -22,8 +22,8 @@ import torch.nn.functional as F
 from . import kernels as K
 from .config import LatentMixerSpec
 
-DECODE_KEYS_PER_SPLIT = 256
-DECODE_MAX_SPLITS = 32
+DECODE_KEYS_PER_SPLIT = 64
+DECODE_MAX_SPLITS = 64
 
 
 def decode_splits(context: int) -> int:

@@ -332,6 +332,36 @@ def test_decode_attention_finds_one_far_key(dtype):
             assert torch.equal(again, got)
 
 
+@pytest.mark.parametrize("H,r", [(16, 512), (5, 96), (20, 64), (1, 32)])
+def test_decode_attention_tensor_core_kernel(H, r):
+    """bf16 with a latent size that is a multiple of 32: sixteen heads per CTA on the tensor cores.  Ragged contexts in slots that
+    are out of order, head counts that do not fill the last tile of sixteen, against fp64 and against the any-size kernel."""
+    k = K()
+    g = torch.Generator().manual_seed(H * r)
+    dk, dv, max_seq = 24, 16, 300
+    ctxs, slots = [1, 33, 64, 65, 300, 129], [4, 0, 5, 2, 1, 3]
+    B = len(ctxs)
+    w_uk = (torch.randn(H * dk, r, generator=g) * r ** -0.5).to(torch.bfloat16)
+    w_uv = (torch.randn(H * dv, r, generator=g) * r ** -0.5).to(torch.bfloat16)
+    cache = torch.randn(6, max_seq, r, generator=g).to(torch.bfloat16)
+    q = (torch.randn(B, H * dk, generator=g) * 2).to(torch.bfloat16)
+    args = (q.cuda(), w_uk.cuda(), w_uv.cuda(), cache.cuda(), torch.tensor(slots, dtype=torch.int32, device="cuda"),
+            torch.tensor([c - 1 for c in ctxs], dtype=torch.int32, device="cuda"), H, dk, dv, 0.3)
+    for splits in (1, 5):
+        got = k.latent_decode(*args, splits)
+        old = k.latent_decode_tune(True)
+        try:
+            plain = k.latent_decode(*args, splits)
+        finally:
+            k.latent_decode_tune(old)
+        for b, (ctx, slot) in enumerate(zip(ctxs, slots)):
+            kk = (cache[slot, :ctx].double() @ w_uk.double().t()).view(ctx, H, dk)
+            v = (cache[slot, :ctx].double() @ w_uv.double().t()).view(ctx, H, dv)
+            want = _attention_reference(q[b].double().view(1, H, dk), kk, v, 0.3, ctx - 1).reshape(1, -1)
+            assert rel_err(got[b : b + 1], want) < 2e-2, (b, splits)
+            assert rel_err(plain[b : b + 1], want) < 2e-2, (b, splits)
+
+
 # ---------------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------------
