@@ -174,4 +174,45 @@ __device__ __forceinline__ void store_from_float<__half>(__half* p, int64_t i, f
 template <>
 __device__ __forceinline__ void store_from_float<float>(float* p, int64_t i, float v) { p[i] = v; }
 
+
+// ---- eight elements at a time (one or two 16-byte accesses); pointers must be 16-byte aligned ------------------------
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+}
+__device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+__device__ __forceinline__ void store8(float* p, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+// true when rows of n elements starting at these addresses can be walked with load8 / store8
+__device__ __forceinline__ bool vec8_ok(int64_t n, const void* a, const void* b = nullptr, const void* c = nullptr, const void* d = nullptr) {
+  return (n & 7) == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+}
+// sum_i a[i] * b[i] over n elements by the 32 lanes of a warp (fp32 accumulation); every lane gets the sum
+template <typename TA, typename TB>
+__device__ __forceinline__ float warp_dot(const TA* __restrict__ a, const TB* __restrict__ b, int n, int lane) {
+  float acc = 0.f;
+  if (vec8_ok(n, a, b)) {
+#pragma unroll 4
+    for (int i = lane * 8; i < n; i += 256) {
+      float x[8], y[8];
+      load8(a + i, x);
+      load8(b + i, y);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(x[j], y[j], acc);
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) acc = fmaf(load_as_float(a, i), load_as_float(b, i), acc);
+  }
+  return warp_sum(acc);
+}
+
 }  // namespace b200

@@ -11,6 +11,7 @@
 //    that average.  Work per cached position is 2 r MACs per head instead of re-expanding dk + dv numbers; the context is
 //    split over CTAs (split-K) and a last kernel merges the splits and applies W_uv.  For bf16 the split runs on the
 //    tensor cores with sixteen heads as the rows of one tile; fp32 models and odd latent sizes take the any-size kernel.
+#include <algorithm>
 #include <type_traits>
 
 #include "mma_tile.cuh"
@@ -184,21 +185,43 @@ __global__ void __launch_bounds__(kLpThreads) latent_prefill_kernel(const T* __r
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kLdThreads = 128, kLdTile = 32, kLdMaxRPT = 8;   // latent size <= 128 * 8
 
-// grid (n_head, batch): q'_h = (W_uk[h]^T q_h) * scale * log2(e), r numbers in fp32 -- the query in latent space
+// grid (n_head, batch): q'_h = (W_uk[h]^T q_h) * scale * log2(e), r numbers in fp32 -- the query in latent space.
+// A thread owns two neighbouring columns of W_uk[h] (dk x r) and one of `groups` slices of its dk rows; the slices are
+// summed through shared memory in a fixed order.
+constexpr int kAbThreads = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(kLdThreads) latent_absorb_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ w_uk,
+__global__ void __launch_bounds__(kAbThreads) latent_absorb_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ w_uk,
                                                                     float* __restrict__ qlat, int dk, int r, float scale_log2) {
-  extern __shared__ __align__(16) float ab_smem[];   // [dk]
+  extern __shared__ __align__(16) float ab_smem[];   // [dk] query, then [groups][2 * ncol] partial sums
   griddep_launch();
   griddep_wait();
   const int h = blockIdx.x, b = blockIdx.y, n_head = gridDim.x, tid = threadIdx.x;
-  for (int d = tid; d < dk; d += kLdThreads) ab_smem[d] = load_as_float(q, (int64_t)b * ldq + (int64_t)h * dk + d);
+  const int ncol = (r + 1) / 2;                                   // column pairs
+  const int groups = ncol >= kAbThreads ? 1 : min(kAbThreads / ncol, dk);
+  float* const part = ab_smem + dk;
+  for (int d = tid; d < dk; d += kAbThreads) ab_smem[d] = load_as_float(q, (int64_t)b * ldq + (int64_t)h * dk + d);
   __syncthreads();
   const T* w = w_uk + (int64_t)h * dk * r;
-  for (int rr = tid; rr < r; rr += kLdThreads) {
-    float acc = 0.f;
+  const int per = (dk + groups - 1) / groups;
+  for (int item = tid; item < groups * ncol; item += kAbThreads) {
+    const int grp = item / ncol, c0 = 2 * (item - grp * ncol);
+    const bool two = c0 + 1 < r;
+    const int d1 = min(dk, (grp + 1) * per);
+    float a0 = 0.f, a1 = 0.f;
 #pragma unroll 8
-    for (int d = 0; d < dk; ++d) acc = fmaf(ab_smem[d], load_as_float(w, (int64_t)d * r + rr), acc);
+    for (int d = grp * per; d < d1; ++d) {
+      const float qd = ab_smem[d];
+      a0 = fmaf(qd, load_as_float(w, (int64_t)d * r + c0), a0);
+      if (two) a1 = fmaf(qd, load_as_float(w, (int64_t)d * r + c0 + 1), a1);
+    }
+    part[grp * 2 * ncol + c0] = a0;
+    part[grp * 2 * ncol + c0 + 1] = a1;
+  }
+  __syncthreads();
+  for (int rr = tid; rr < r; rr += kAbThreads) {
+    float acc = 0.f;
+    for (int g = 0; g < groups; ++g) acc += part[g * 2 * ncol + rr];
     qlat[((int64_t)b * n_head + h) * r + rr] = acc * scale_log2;
   }
 }
@@ -405,8 +428,10 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const flo
 }
 
 // grid (n_head, batch): merge the splits, then out_h = W_uv[h] (sum_j p_j c_j)
+constexpr int kLmThreads = 256;
+
 template <typename T>
-__global__ void __launch_bounds__(kLdThreads) latent_decode_merge_kernel(const float* __restrict__ ws, const T* __restrict__ w_uv,
+__global__ void __launch_bounds__(kLmThreads) latent_decode_merge_kernel(const float* __restrict__ ws, const T* __restrict__ w_uv,
                                                                           T* __restrict__ out, int64_t ldo, int n_head, int dv, int r,
                                                                           int n_split) {
   extern __shared__ __align__(16) float lm_smem[];   // [r] averaged latent, [n_split] weights
@@ -428,17 +453,15 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_merge_kernel(const f
   }
   __syncthreads();
   const float inv = 1.0f / tot;
-  for (int rr = tid; rr < r; rr += kLdThreads) {
+  for (int rr = tid; rr < r; rr += kLmThreads) {
     float acc = 0.f;
+#pragma unroll 8
     for (int s = 0; s < n_split; ++s) acc = fmaf(wgt[s], src[(int64_t)s * (r + 2) + rr], acc);
     avg[rr] = acc * inv;
   }
   __syncthreads();
-  for (int c = warp; c < dv; c += kLdThreads / 32) {
-    const T* wr = w_uv + ((int64_t)h * dv + c) * r;
-    float dot = 0.f;
-    for (int rr = lane; rr < r; rr += 32) dot = fmaf(load_as_float(wr, rr), avg[rr], dot);
-    dot = warp_sum(dot);
+  for (int c = warp; c < dv; c += kLmThreads / 32) {
+    const float dot = warp_dot(w_uv + ((int64_t)h * dv + c) * r, avg, r, lane);
     if (lane == 0) store_from_float(out, (int64_t)b * ldo + (int64_t)h * dv + c, dot);
   }
 }
@@ -464,7 +487,9 @@ std::atomic<int> g_decode_simt{0};   // test knob: keep bf16 decode on the any-s
 
 template <typename T>
 int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
-  const size_t smem0 = (size_t)a->dk * sizeof(float);
+  const int ab_ncol = (a->r + 1) / 2;
+  const int ab_groups = ab_ncol >= kAbThreads ? 1 : std::min(kAbThreads / ab_ncol, a->dk);
+  const size_t smem0 = ((size_t)a->dk + (size_t)ab_groups * 2 * ab_ncol) * sizeof(float);
   const size_t smem1 = (size_t)(a->r + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * a->r * sizeof(T);
   const size_t smem2 = (size_t)(a->r + a->n_split) * sizeof(float);
   const size_t smem3 = (size_t)((kLmHeads + kLdTile) * (a->r + 8) + kLmHeads * 40) * 2 + 8 * kLmHeads * sizeof(float);
@@ -479,7 +504,7 @@ int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
   float* qlat = (float*)a->workspace;
   float* parts = qlat + (size_t)a->batch * a->n_head * a->r;
   const float scale_log2 = a->scale * 1.4426950408889634f;
-  B200_CUDA(launch(latent_absorb_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem0, st, (const T*)a->q, a->ldq,
+  B200_CUDA(launch(latent_absorb_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kAbThreads), smem0, st, (const T*)a->q, a->ldq,
                    (const T*)a->w_uk, qlat, a->dk, a->r, scale_log2));
   const bool tensor = std::is_same<T, __nv_bfloat16>::value && a->r % 32 == 0 && a->r <= 32 * kLmMaxNT && !g_decode_simt.load() &&
                       (reinterpret_cast<uintptr_t>(a->cache) & 15) == 0 && (a->slot_stride & 7) == 0;
@@ -490,7 +515,7 @@ int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
   else
     B200_CUDA(launch(latent_decode_split_kernel<T>, dim3((unsigned)a->n_split, (unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem1, st,
                      (const float*)qlat, (const T*)a->cache, a->slot_stride, a->row_slot, a->row_pos, parts, a->n_head, a->r, a->max_seq));
-  B200_CUDA(launch(latent_decode_merge_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem2, st,
+  B200_CUDA(launch(latent_decode_merge_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kLmThreads), smem2, st,
                    (const float*)parts, (const T*)a->w_uv, (T*)a->out, a->ldo, a->n_head, a->dv, a->r, a->n_split));
   return B200_OK;
 }

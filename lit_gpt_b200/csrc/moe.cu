@@ -14,7 +14,7 @@ namespace b200 {
 
 namespace {
 
-constexpr int kRtThreads = 128;
+constexpr int kRtThreads = 256;
 
 // argmax over v[0..n) by the 32 lanes of a warp: largest value, lowest index among equals; every lane gets the index
 __device__ __forceinline__ int warp_argmax(const float* v, int n, int lane) {
@@ -48,10 +48,7 @@ __global__ void __launch_bounds__(kRtThreads) moe_route_kernel(const T* __restri
   const int64_t t = blockIdx.x;
   const T* xr = x + t * d;
   for (int e = warp; e < n_expert; e += kRtThreads / 32) {
-    const T* wr = w_router + (int64_t)e * d;
-    float z = 0.f;
-    for (int i = lane; i < d; i += 32) z = fmaf(load_as_float(xr, i), load_as_float(wr, i), z);
-    z = warp_sum(z);
+    const float z = warp_dot(xr, w_router + (int64_t)e * d, d, lane);
     if (lane == 0) {
       const float s = 1.0f / (1.0f + expf(-z));
       score[e] = s;
@@ -218,9 +215,7 @@ __global__ void __launch_bounds__(256) moe_gemv_up_kernel(const T* __restrict__ 
   if (f >= ff) return;
   const T* xr = x + (int64_t)(p / top) * d;
   const T* wr = w_up + ((int64_t)ids[p] * ff + f) * d;
-  float acc = 0.f;
-  for (int i = lane; i < d; i += 32) acc = fmaf(load_as_float(wr, i), load_as_float(xr, i), acc);
-  acc = warp_sum(acc);
+  float acc = warp_dot(wr, xr, d, lane);
   if (lane == 0) {
     acc = fmaxf(acc, 0.f);
     store_from_float(hidden, (int64_t)p * ff + f, acc * acc);
@@ -242,9 +237,7 @@ __global__ void __launch_bounds__(256) moe_gemv_down_kernel(const T* __restrict_
     const int p = t * top + k;
     const T* hr = hidden + (int64_t)p * ff;
     const T* wr = w_down + ((int64_t)ids[p] * d + c) * ff;
-    float acc = 0.f;
-    for (int i = lane; i < ff; i += 32) acc = fmaf(load_as_float(wr, i), load_as_float(hr, i), acc);
-    acc = warp_sum(acc);
+    const float acc = warp_dot(wr, hr, ff, lane);
     T rounded;   // the expert's output takes the matrix-product dtype before it is weighted, as in the grouped path
     store_from_float(&rounded, 0, acc);
     total = fmaf(wts[p], load_as_float(&rounded, 0), total);
@@ -258,6 +251,20 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const T* __restrict__ 
   griddep_launch();
   griddep_wait();
   const int64_t t = blockIdx.x;
+  if (vec8_ok(d, y, out)) {
+    for (int c = threadIdx.x * 8; c < d; c += 128 * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < top; ++k) {
+        float v[8];
+        load8(y + (int64_t)slot_of[t * top + k] * d + c, v);
+        const float w = wts[t * top + k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, v[j], acc[j]);
+      }
+      store8(out + t * d + c, acc);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < d; c += 128) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], load_as_float(y, (int64_t)slot_of[t * top + k] * d + c), acc);

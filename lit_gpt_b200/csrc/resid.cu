@@ -73,15 +73,34 @@ __global__ void __launch_bounds__(kRowThreads) rms_rows_kernel(RmsSeg s0, RmsSeg
   const TI* xr = reinterpret_cast<const TI*>(s.in) + irow * s.ld_in;
   const TO* w = reinterpret_cast<const TO*>(s.weight);
   TO* yr = reinterpret_cast<TO*>(s.out) + orow * s.ld_out;
+  const bool vec = vec8_ok(s.d, xr, w, yr);
+  const float one = s.plus_one ? 1.0f : 0.0f;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < s.d; i += kRowThreads) {
-    const float v = load_as_float(xr, i);
-    ss = fmaf(v, v, ss);
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < s.d; i += kRowThreads * 8) {
+      float v[8];
+      load8(xr + i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < s.d; i += kRowThreads) {
+      const float v = load_as_float(xr, i);
+      ss = fmaf(v, v, ss);
+    }
   }
   const float rstd = 1.0f / sqrtf(cta_sum(ss, s_part) / (float)s.d + eps);
-  for (int i = threadIdx.x; i < s.d; i += kRowThreads) {
-    const float g = load_as_float(w, i) + (s.plus_one ? 1.0f : 0.0f);
-    store_from_float(yr, i, load_as_float(xr, i) * rstd * g);
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < s.d; i += kRowThreads * 8) {
+      float v[8], g[8];
+      load8(xr + i, v);
+      load8(w + i, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = v[j] * rstd * (g[j] + one);
+      store8(yr + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < s.d; i += kRowThreads) store_from_float(yr, i, load_as_float(xr, i) * rstd * (load_as_float(w, i) + one));
   }
 }
 
@@ -94,16 +113,41 @@ __global__ void __launch_bounds__(kRowThreads) residual_norm_add_kernel(const T*
   griddep_wait();
   const int64_t row = blockIdx.x;
   const T* yr = y + row * d;
+  float* xr = x + row * d;
+  T* ar = act + row * d;
+  const bool vec = vec8_ok(d, yr, w, xr, ar);
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += kRowThreads) {
-    const float v = load_as_float(yr, i);
-    ss = fmaf(v, v, ss);
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < d; i += kRowThreads * 8) {
+      float v[8];
+      load8(yr + i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += kRowThreads) {
+      const float v = load_as_float(yr, i);
+      ss = fmaf(v, v, ss);
+    }
   }
   const float rstd = 1.0f / sqrtf(cta_sum(ss, s_part) / (float)d + eps);
-  for (int i = threadIdx.x; i < d; i += kRowThreads) {
-    const float v = x[row * d + i] + load_as_float(yr, i) * rstd * (1.0f + load_as_float(w, i));
-    x[row * d + i] = v;
-    store_from_float(act, row * d + i, v);
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < d; i += kRowThreads * 8) {
+      float v[8], g[8], r[8];
+      load8(yr + i, v);
+      load8(w + i, g);
+      load8(xr + i, r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) r[j] = r[j] + v[j] * rstd * (1.0f + g[j]);
+      store8(xr + i, r);
+      store8(ar + i, r);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += kRowThreads) {
+      const float v = xr[i] + load_as_float(yr, i) * rstd * (1.0f + load_as_float(w, i));
+      xr[i] = v;
+      store_from_float(ar, i, v);
+    }
   }
 }
 
@@ -113,7 +157,14 @@ __global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(const T* __res
   griddep_launch();
   griddep_wait();
   const int64_t r = (int64_t)rows[blockIdx.x];
-  for (int i = threadIdx.x; i < d; i += kRowThreads) dst[(int64_t)blockIdx.x * d + i] = src[r * d + i];
+  const T* sr = src + r * d;
+  T* dr = dst + (int64_t)blockIdx.x * d;
+  if (vec8_ok((int64_t)d * sizeof(T) / 2, sr, dr)) {   // whole 16-byte pieces
+    const int n16 = d * (int)sizeof(T) / 16;
+    for (int i = threadIdx.x; i < n16; i += kRowThreads) reinterpret_cast<uint4*>(dr)[i] = reinterpret_cast<const uint4*>(sr)[i];
+  } else {
+    for (int i = threadIdx.x; i < d; i += kRowThreads) dr[i] = sr[i];
+  }
 }
 
 // x = relu(x)^2 in place
@@ -121,6 +172,16 @@ template <typename T>
 __global__ void __launch_bounds__(256) sqrelu_kernel(T* __restrict__ x, int64_t n) {
   griddep_launch();
   griddep_wait();
+  if (vec8_ok(n, x)) {
+    for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 8; i < n; i += (int64_t)gridDim.x * 2048) {
+      float v[8];
+      load8(x + i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[j] = fmaxf(v[j], 0.f); v[j] *= v[j]; }
+      store8(x + i, v);
+    }
+    return;
+  }
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
     const float v = fmaxf(load_as_float(x, i), 0.f);
     store_from_float(x, i, v * v);
