@@ -280,6 +280,8 @@ def main(
     from lit_gpt_b200.tokenizer import Tokenizer
 
     precision = precision or get_default_supported_precision(training=False)
+    if (checkpoint_dir / "config.json").is_file() and not (checkpoint_dir / "lit_config.json").is_file():
+        return _main_registered(prompt, num_samples, max_new_tokens, top_k, temperature, checkpoint_dir, quantize, precision)
 
     plugins = None
     if quantize is not None:
@@ -328,6 +330,51 @@ def main(
         fabric.print(
             f"Time for inference {i + 1}: {t:.02f} sec total, {tokens_generated / t:.02f} tokens/sec", file=sys.stderr
         )
+    if fabric.device.type == "cuda":
+        fabric.print(f"Memory used: {torch.cuda.max_memory_allocated() / 1e9:.02f} GB", file=sys.stderr)
+
+
+def _main_registered(prompt: str, num_samples: int, max_new_tokens: int, top_k: Optional[int], temperature: float, checkpoint_dir: Path,
+                     quantize: Optional[str], precision: str) -> None:
+    """`main` for a checkpoint directory with a ``config.json`` whose architecture is registered in ``lit_gpt_b200.config``
+    (``model.safetensors`` weights).  Without tokenizer files the prompt is a list of token ids ("3 17 250" or "3,17,250") and
+    ids are printed."""
+    from lit_gpt_b200.config import load_config, model_class
+    from lit_gpt_b200.pomipel import Pomipel, load_pomipel
+
+    if quantize is not None:
+        raise ValueError("Quantization is not supported for this architecture.")
+    dtype = {"bf16-true": torch.bfloat16, "32-true": torch.float32}.get(precision)
+    if dtype is None:
+        raise ValueError(f"--precision {precision!r}: this architecture runs in bf16-true or 32-true")
+    config = load_config(checkpoint_dir)
+    if model_class(config) is not Pomipel:
+        raise ValueError(f"no generate entry point for {type(config).__name__}")
+    fabric = Fabric(devices=1, precision=precision)
+    has_tokenizer = (checkpoint_dir / "tokenizer.json").is_file() or (checkpoint_dir / "tokenizer.model").is_file()
+    if has_tokenizer:
+        from lit_gpt_b200.tokenizer import Tokenizer
+
+        tokenizer = Tokenizer(checkpoint_dir)
+        encoded = tokenizer.encode(prompt, device=fabric.device)
+        eos_id = tokenizer.eos_id
+    else:
+        encoded = torch.tensor([int(t) for t in prompt.replace(",", " ").split()], dtype=torch.int64, device=fabric.device)
+        tokenizer, eos_id = None, None
+    max_returned_tokens = encoded.size(0) + max_new_tokens
+    t0 = time.perf_counter()
+    model = load_pomipel(checkpoint_dir, dtype=dtype, device=fabric.device)
+    model.max_seq_length = min(max_returned_tokens, config.block_size)
+    model.set_kv_cache(batch_size=1)
+    fabric.print(f"Time to load the model weights: {time.perf_counter() - t0:.02f} seconds.", file=sys.stderr)
+    seed_everything(1234)
+    for i in range(num_samples):
+        t0 = time.perf_counter()
+        y = generate(model, encoded, max_returned_tokens, temperature=temperature, top_k=top_k, eos_id=eos_id)
+        t = time.perf_counter() - t0
+        fabric.print(tokenizer.decode(y) if tokenizer is not None else " ".join(str(int(v)) for v in y))
+        n = y.size(0) - encoded.size(0)
+        fabric.print(f"Time for inference {i + 1}: {t:.02f} sec total, {n / t:.02f} tokens/sec", file=sys.stderr)
     if fabric.device.type == "cuda":
         fabric.print(f"Memory used: {torch.cuda.max_memory_allocated() / 1e9:.02f} GB", file=sys.stderr)
 
