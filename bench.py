@@ -590,10 +590,18 @@ def run_arch_compare(args) -> None:
                                             "bytes": 2.0 * B * H * ctx * hs * 2}
             x = torch.randn(T, d, device=dev, dtype=torch.bfloat16)
             ms = _timed(lambda: pom.blocks[0].mlp(x), iters, flush)
-            kern["feed_forward_pomipel"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * top * ff * d / (ms * 1e-3) / tf}
+            # bytes: every expert's two matrices once (T * top >= E: all are touched), the gathered rows, the hidden rows and the
+            # per-choice outputs each written and read back; the dense layer below: three matrices and its own intermediates
+            moe_bytes = 2.0 * E * ff * d * 2 + T * top * (2 * d * 2 + 4 * ff * 2 + 2 * d * 2) + 2 * T * d * 2
+            roof = max(4.0 * T * top * ff * d / tf, moe_bytes / hbm)
+            kern["feed_forward_pomipel"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * top * ff * d / (ms * 1e-3) / tf,
+                                            "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": moe_bytes}
             x3 = x.view(1, T, d)
             ms = _timed(lambda: gpt.transformer.h[0].mlp(x3), iters, flush)
-            kern["feed_forward_gpt"] = {"ms": ms, "frac_of_measured_bf16": 6.0 * T * inter * d / (ms * 1e-3) / tf}
+            mlp_bytes = 3.0 * inter * d * 2 + T * (2 * d * 2 + 5 * inter * 2)
+            roof = max(6.0 * T * inter * d / tf, mlp_bytes / hbm)
+            kern["feed_forward_gpt"] = {"ms": ms, "frac_of_measured_bf16": 6.0 * T * inter * d / (ms * 1e-3) / tf,
+                                        "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": mlp_bytes}
             xs, act, w0 = torch.randn(T, d, device=dev), torch.empty(T, d, device=dev, dtype=torch.bfloat16), pom.blocks[0].norm_1
             ms = _timed(lambda: K.residual_norm_add(x, w0, 1e-5, xs, act), iters, flush)
             kern["residual_norm_pomipel"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}

@@ -188,8 +188,11 @@ constexpr int kLdThreads = 128, kLdTile = 32, kLdMaxRPT = 8;   // latent size <=
 // grid (n_head, batch): q'_h = (W_uk[h]^T q_h) * scale * log2(e), r numbers in fp32 -- the query in latent space.
 // A thread owns two neighbouring columns of W_uk[h] (dk x r) and one of `groups` slices of its dk rows; the slices are
 // summed through shared memory in a fixed order.
-constexpr int kAbThreads = 512;
+constexpr int kAbThreads = 512, kAbMaxChunks = 4;
 
+__host__ __device__ inline int absorb_chunks(int r) { return max(1, min(kAbMaxChunks, (r + 1) / 2 / 32)); }
+
+// grid (n_head, batch, absorb_chunks(r)): every CTA takes a range of column pairs
 template <typename T>
 __global__ void __launch_bounds__(kAbThreads) latent_absorb_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ w_uk,
                                                                     float* __restrict__ qlat, int dk, int r, float scale_log2) {
@@ -197,7 +200,9 @@ __global__ void __launch_bounds__(kAbThreads) latent_absorb_kernel(const T* __re
   griddep_launch();
   griddep_wait();
   const int h = blockIdx.x, b = blockIdx.y, n_head = gridDim.x, tid = threadIdx.x;
-  const int ncol = (r + 1) / 2;                                   // column pairs
+  const int all_pairs = (r + 1) / 2;
+  const int ncol = (all_pairs + (int)gridDim.z - 1) / (int)gridDim.z;     // column pairs of this CTA
+  const int pair0 = (int)blockIdx.z * ncol;
   const int groups = ncol >= kAbThreads ? 1 : min(kAbThreads / ncol, dk);
   float* const part = ab_smem + dk;
   for (int d = tid; d < dk; d += kAbThreads) ab_smem[d] = load_as_float(q, (int64_t)b * ldq + (int64_t)h * dk + d);
@@ -205,23 +210,27 @@ __global__ void __launch_bounds__(kAbThreads) latent_absorb_kernel(const T* __re
   const T* w = w_uk + (int64_t)h * dk * r;
   const int per = (dk + groups - 1) / groups;
   for (int item = tid; item < groups * ncol; item += kAbThreads) {
-    const int grp = item / ncol, c0 = 2 * (item - grp * ncol);
-    const bool two = c0 + 1 < r;
+    const int grp = item / ncol, lc = item - grp * ncol, c0 = 2 * (pair0 + lc);
+    const bool one = c0 < r, two = c0 + 1 < r;
     const int d1 = min(dk, (grp + 1) * per);
     float a0 = 0.f, a1 = 0.f;
+    if (one) {
 #pragma unroll 8
-    for (int d = grp * per; d < d1; ++d) {
-      const float qd = ab_smem[d];
-      a0 = fmaf(qd, load_as_float(w, (int64_t)d * r + c0), a0);
-      if (two) a1 = fmaf(qd, load_as_float(w, (int64_t)d * r + c0 + 1), a1);
+      for (int d = grp * per; d < d1; ++d) {
+        const float qd = ab_smem[d];
+        a0 = fmaf(qd, load_as_float(w, (int64_t)d * r + c0), a0);
+        if (two) a1 = fmaf(qd, load_as_float(w, (int64_t)d * r + c0 + 1), a1);
+      }
     }
-    part[grp * 2 * ncol + c0] = a0;
-    part[grp * 2 * ncol + c0 + 1] = a1;
+    part[grp * 2 * ncol + 2 * lc] = a0;
+    part[grp * 2 * ncol + 2 * lc + 1] = a1;
   }
   __syncthreads();
-  for (int rr = tid; rr < r; rr += kAbThreads) {
+  for (int lc = tid; lc < 2 * ncol; lc += kAbThreads) {
+    const int rr = 2 * pair0 + lc;
+    if (rr >= r) continue;
     float acc = 0.f;
-    for (int g = 0; g < groups; ++g) acc += part[g * 2 * ncol + rr];
+    for (int g = 0; g < groups; ++g) acc += part[g * 2 * ncol + lc];
     qlat[((int64_t)b * n_head + h) * r + rr] = acc * scale_log2;
   }
 }
@@ -427,31 +436,34 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const flo
   }
 }
 
-// grid (n_head, batch): merge the splits, then out_h = W_uv[h] (sum_j p_j c_j)
+// grid (n_head, batch, chunks of the value rows): merge the splits, then out_h = W_uv[h] (sum_j p_j c_j)
 constexpr int kLmThreads = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(kLmThreads) latent_decode_merge_kernel(const float* __restrict__ ws, const T* __restrict__ w_uv,
                                                                           T* __restrict__ out, int64_t ldo, int n_head, int dv, int r,
                                                                           int n_split) {
-  extern __shared__ __align__(16) float lm_smem[];   // [r] averaged latent, [n_split] weights
+  extern __shared__ __align__(16) float lm_smem[];   // [r] averaged latent, [n_split] weights, maxima, sums
   griddep_launch();
   griddep_wait();
   float* const avg = lm_smem;
-  float* const wgt = avg + r;
+  float* const wgt = avg + ((r + 3) & ~3);
+  float* const smx = wgt + n_split;
+  float* const ssm = smx + n_split;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.x, b = blockIdx.y;
   const float* src = ws + ((int64_t)b * n_head + h) * n_split * (r + 2);
-  float mx = -INFINITY;
-  for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, src[(int64_t)s * (r + 2) + r]);
-  float tot = 0.f;
-  for (int s = 0; s < n_split; ++s) {
-    const float m = src[(int64_t)s * (r + 2) + r];
-    const float w = m == -INFINITY ? 0.f : exp2f(m - mx);
-    tot = fmaf(w, src[(int64_t)s * (r + 2) + r + 1], tot);
-    if (tid == 0) wgt[s] = w;
+  for (int s = tid; s < n_split; s += kLmThreads) {
+    smx[s] = src[(int64_t)s * (r + 2) + r];
+    ssm[s] = src[(int64_t)s * (r + 2) + r + 1];
   }
   __syncthreads();
+  float mx = -INFINITY;
+  for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, smx[s]);
+  for (int s = tid; s < n_split; s += kLmThreads) wgt[s] = smx[s] == -INFINITY ? 0.f : exp2f(smx[s] - mx);
+  __syncthreads();
+  float tot = 0.f;
+  for (int s = 0; s < n_split; ++s) tot = fmaf(wgt[s], ssm[s], tot);
   const float inv = 1.0f / tot;
   for (int rr = tid; rr < r; rr += kLmThreads) {
     float acc = 0.f;
@@ -460,7 +472,11 @@ __global__ void __launch_bounds__(kLmThreads) latent_decode_merge_kernel(const f
     avg[rr] = acc * inv;
   }
   __syncthreads();
-  for (int c = warp; c < dv; c += kLmThreads / 32) {
+  // this CTA's share of the head's value rows (gridDim.z CTAs per head)
+  const int per = (dv + (int)gridDim.z - 1) / (int)gridDim.z;
+  const int c_lo = (int)blockIdx.z * per, c_hi = min(dv, c_lo + per);
+#pragma unroll 2
+  for (int c = c_lo + warp; c < c_hi; c += kLmThreads / 32) {
     const float dot = warp_dot(w_uv + ((int64_t)h * dv + c) * r, avg, r, lane);
     if (lane == 0) store_from_float(out, (int64_t)b * ldo + (int64_t)h * dv + c, dot);
   }
@@ -487,11 +503,13 @@ std::atomic<int> g_decode_simt{0};   // test knob: keep bf16 decode on the any-s
 
 template <typename T>
 int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
-  const int ab_ncol = (a->r + 1) / 2;
+  const int ab_chunks = absorb_chunks(a->r);
+  const int ab_ncol = ((a->r + 1) / 2 + ab_chunks - 1) / ab_chunks;
   const int ab_groups = ab_ncol >= kAbThreads ? 1 : std::min(kAbThreads / ab_ncol, a->dk);
   const size_t smem0 = ((size_t)a->dk + (size_t)ab_groups * 2 * ab_ncol) * sizeof(float);
   const size_t smem1 = (size_t)(a->r + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * a->r * sizeof(T);
-  const size_t smem2 = (size_t)(a->r + a->n_split) * sizeof(float);
+  const size_t smem2 = (size_t)(a->r + 4 + 3 * a->n_split) * sizeof(float);
+  const int merge_chunks = std::max(1, std::min(4, a->dv / 32));
   const size_t smem3 = (size_t)((kLmHeads + kLdTile) * (a->r + 8) + kLmHeads * 40) * 2 + 8 * kLmHeads * sizeof(float);
   B200_CHECK_ARG(smem0 <= 48 * 1024 && smem1 <= 227 * 1024 && smem2 <= 227 * 1024, "b200_latent_decode: sizes need too much shared memory");
   static PerDeviceOnce once;
@@ -504,7 +522,7 @@ int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
   float* qlat = (float*)a->workspace;
   float* parts = qlat + (size_t)a->batch * a->n_head * a->r;
   const float scale_log2 = a->scale * 1.4426950408889634f;
-  B200_CUDA(launch(latent_absorb_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kAbThreads), smem0, st, (const T*)a->q, a->ldq,
+  B200_CUDA(launch(latent_absorb_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch, (unsigned)ab_chunks), dim3(kAbThreads), smem0, st, (const T*)a->q, a->ldq,
                    (const T*)a->w_uk, qlat, a->dk, a->r, scale_log2));
   const bool tensor = std::is_same<T, __nv_bfloat16>::value && a->r % 32 == 0 && a->r <= 32 * kLmMaxNT && !g_decode_simt.load() &&
                       (reinterpret_cast<uintptr_t>(a->cache) & 15) == 0 && (a->slot_stride & 7) == 0;
@@ -515,7 +533,7 @@ int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
   else
     B200_CUDA(launch(latent_decode_split_kernel<T>, dim3((unsigned)a->n_split, (unsigned)a->n_head, (unsigned)a->batch), dim3(kLdThreads), smem1, st,
                      (const float*)qlat, (const T*)a->cache, a->slot_stride, a->row_slot, a->row_pos, parts, a->n_head, a->r, a->max_seq));
-  B200_CUDA(launch(latent_decode_merge_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch), dim3(kLmThreads), smem2, st,
+  B200_CUDA(launch(latent_decode_merge_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->batch, (unsigned)merge_chunks), dim3(kLmThreads), smem2, st,
                    (const float*)parts, (const T*)a->w_uv, (T*)a->out, a->ldo, a->n_head, a->dv, a->r, a->n_split));
   return B200_OK;
 }
