@@ -576,7 +576,7 @@ def run_arch_compare(args) -> None:
             slot = torch.arange(B, dtype=torch.int32, device=dev)
             rp = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
             from lit_gpt_b200.latent import decode_splits
-            ms = _timed(lambda: K.latent_decode(qd, mx.w_uk, mx.w_uv, cache, slot, rp, H, hs, hs, hs ** -0.5, decode_splits(ctx)), iters, flush)
+            ms = _timed(lambda: K.latent_decode(qd, mx.w_uk, mx.w_uv, cache, slot, rp, H, hs, hs, hs ** -0.5, decode_splits(ctx, B * (-(-H // 16)))), iters, flush)
             roof = max(B * ctx * r * 2 / hbm, 4.0 * B * H * ctx * r / tf)
             kern["decode_attention_pomipel"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3),
                                                 "bytes": B * ctx * r * 2, "flops": 4.0 * B * H * ctx * r}

@@ -330,8 +330,8 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const flo
   griddep_wait();
   const int pitch = r + 8;                                              // bf16 elements; rows stay 16-byte aligned and spread over the banks
   __nv_bfloat16* const Qs = reinterpret_cast<__nv_bfloat16*>(lm_smem_raw);   // [16][pitch]
-  __nv_bfloat16* const Cs = Qs + kLmHeads * pitch;                            // [32][pitch]
-  __nv_bfloat16* const Ps = Cs + kLdTile * pitch;                             // [16][40]
+  __nv_bfloat16* const Cbuf = Qs + kLmHeads * pitch;                          // [2][32][pitch]: the tile in use and the next one
+  __nv_bfloat16* const Ps = Cbuf + 2 * kLdTile * pitch;                       // [16][40]
   float* const smax = reinterpret_cast<float*>(Ps + kLmHeads * 40);          // [4][16]
   float* const ssum = smax + 4 * kLmHeads;                                    // [4][16]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
@@ -345,25 +345,34 @@ __global__ void __launch_bounds__(kLdThreads) latent_decode_mma_kernel(const flo
   const int nt = r / 32;                                                 // 8-column tiles of the latent sum per warp
   const int chunks = r / 8;                                              // 16-byte chunks per latent
 
-  for (int idx = tid; idx < kLmHeads * r; idx += kLdThreads) {
-    const int hh = idx / r, rr = idx - hh * r;
-    Qs[hh * pitch + rr] = __float2bfloat16_rn(h0 + hh < n_head ? qlat[((int64_t)b * n_head + h0 + hh) * r + rr] : 0.f);
+  auto load_tile = [&](int j0, int buf) {
+    const int nj = min(kLdTile, k1 - j0);
+    __nv_bfloat16* dst = Cbuf + buf * kLdTile * pitch;
+    for (int idx = tid; idx < kLdTile * chunks; idx += kLdThreads) {
+      const int j = idx / chunks, c = idx - j * chunks;
+      pf_cp16(pf_smem(dst + j * pitch + c * 8), crow + (int64_t)(j0 + (j < nj ? j : 0)) * r + c * 8, j < nj);
+    }
+    pf_commit();
+  };
+  if (k0 < k1) load_tile(k0, 0);
+  for (int idx = tid; idx < kLmHeads * (r / 4); idx += kLdThreads) {     // q' of the sixteen heads, four values at a time
+    const int hh = idx / (r / 4), c4 = idx - hh * (r / 4);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (h0 + hh < n_head) v = *reinterpret_cast<const float4*>(qlat + ((int64_t)b * n_head + h0 + hh) * r + 4 * c4);
+    *reinterpret_cast<uint2*>(Qs + hh * pitch + 4 * c4) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
   }
   float o[kLmMaxNT][4];
 #pragma unroll
   for (int i = 0; i < kLmMaxNT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;             // rows g and g + 8, identical in every warp
 
-  for (int j0 = k0; j0 < k1; j0 += kLdTile) {
-    __syncthreads();                                                     // previous tile consumed; Qs visible on the first pass
+  int buf = 0;
+  for (int j0 = k0; j0 < k1; j0 += kLdTile, buf ^= 1) {
+    __syncthreads();                                                     // the other buffer is free again; Qs visible on the first pass
     const int nj = min(kLdTile, k1 - j0);
-    for (int idx = tid; idx < kLdTile * chunks; idx += kLdThreads) {
-      const int j = idx / chunks, c = idx - j * chunks;
-      pf_cp16(pf_smem(Cs + j * pitch + c * 8), crow + (int64_t)(j0 + (j < nj ? j : 0)) * r + c * 8, j < nj);
-    }
-    pf_commit();
-    pf_wait<0>();
+    if (j0 + kLdTile < k1) { load_tile(j0 + kLdTile, buf ^ 1); pf_wait<1>(); } else { pf_wait<0>(); }
     __syncthreads();
+    const __nv_bfloat16* Cs = Cbuf + buf * kLdTile * pitch;
     // scores of this warp's eight keys for the sixteen heads
     float sacc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int ks = 0; ks < r / 32; ++ks) {
@@ -510,7 +519,7 @@ int decode_launch(const b200_latent_decode_args* a, cudaStream_t st) {
   const size_t smem1 = (size_t)(a->r + kLdTile + 4) * sizeof(float) + (size_t)kLdTile * a->r * sizeof(T);
   const size_t smem2 = (size_t)(a->r + 4 + 3 * a->n_split) * sizeof(float);
   const int merge_chunks = std::max(1, std::min(4, a->dv / 32));
-  const size_t smem3 = (size_t)((kLmHeads + kLdTile) * (a->r + 8) + kLmHeads * 40) * 2 + 8 * kLmHeads * sizeof(float);
+  const size_t smem3 = (size_t)((kLmHeads + 2 * kLdTile) * (a->r + 8) + kLmHeads * 40) * 2 + 8 * kLmHeads * sizeof(float);
   B200_CHECK_ARG(smem0 <= 48 * 1024 && smem1 <= 227 * 1024 && smem2 <= 227 * 1024, "b200_latent_decode: sizes need too much shared memory");
   static PerDeviceOnce once;
   if (once.need()) {

@@ -26,9 +26,13 @@ DECODE_KEYS_PER_SPLIT = 64
 DECODE_MAX_SPLITS = 64
 
 
-def decode_splits(context: int) -> int:
-    """CTAs that share one (sequence, head) of a decode step over a context of at most `context` positions."""
-    return max(1, min(DECODE_MAX_SPLITS, -(-context // DECODE_KEYS_PER_SPLIT)))
+DECODE_TARGET_CTAS = 296   # two per SM
+
+
+def decode_splits(context: int, rows: int = 1) -> int:
+    """CTAs that share one (sequence, head tile) of a decode step over a context of at most `context` positions: 64-key ranges,
+    but no more splits than it takes `rows` (sequences x head tiles) to fill the GPU twice."""
+    return max(1, min(DECODE_MAX_SPLITS, -(-context // DECODE_KEYS_PER_SPLIT), max(1, DECODE_TARGET_CTAS // max(rows, 1))))
 
 
 @dataclass
@@ -106,8 +110,9 @@ class LatentAttention(nn.Module):
         K.rms_rows(n, self.eps, *segs, in_dtype=h.dtype, out_dtype=h.dtype, device=h.device)
         q = F.linear(cq, self.w_uq)
         if batch.decode:
+            tiles = -(-H // 16) if h.dtype == torch.bfloat16 and s.kv_rank % 32 == 0 and s.kv_rank <= 512 else H
             y = K.latent_decode(q, self.w_uk, self.w_uv, cache.latents, batch.row_slot, batch.row_pos, H, s.dim, s.vdim, s.scale,
-                                decode_splits(batch.context_hint))
+                                decode_splits(batch.context_hint, n * tiles))
         else:
             key = id(self.source)
             ctx = shared.get(key)
