@@ -56,6 +56,14 @@ CFG_WIDE = config(width=128, vocab=200, layers=[
 ], max_positions=1100)
 
 
+# nothing divisible by four, not even the width: every kernel on its element-by-element path, odd leading dimensions in the GEMMs
+CFG_RAGGED_SIZES = config(width=70, vocab=97, layers=[
+    (mixer(2, 10, 6, 14, 9), moe(5, 2, 11, 1, 1)),
+    (mixer(3, 6, 10, 14, 7, scale=0.5, kv_from=0), moe(6, 3, 9, 3, 2)),
+    (mixer(1, 7, 7, 22, 5), None),
+], max_positions=130, emb_scale=1.7, logit_scale=1.3, eps=1e-3)
+
+
 def checkpoint(cfg, seed, gain=1.0):
     g = torch.Generator().manual_seed(seed)
 
@@ -365,7 +373,7 @@ def test_decode_attention_tensor_core_kernel(H, r):
 # ---------------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("cfg,seed", [(CFG_ODD, 11), (CFG_WIDE, 12)])
+@pytest.mark.parametrize("cfg,seed", [(CFG_ODD, 11), (CFG_WIDE, 12), (CFG_RAGGED_SIZES, 13)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prompt_matches_oracle(cfg, seed, dtype):
     w = checkpoint(cfg, seed)
@@ -396,9 +404,9 @@ def test_layers_follow_the_oracle_one_by_one():
         assert rel_err(x, layers[i]) < 1e-5, f"residual stream after layer {i}"
 
 
+@pytest.mark.parametrize("cfg", [CFG_ODD, CFG_RAGGED_SIZES])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_decoding_token_by_token_equals_prefill(dtype):
-    cfg = CFG_ODD
+def test_decoding_token_by_token_equals_prefill(dtype, cfg):
     w = checkpoint(cfg, 31)
     model = build(cfg, w, dtype)
     toks = tokens_for(cfg, 45, 31)
