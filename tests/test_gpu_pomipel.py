@@ -533,3 +533,54 @@ def test_forward_signature_of_the_other_models():
         out = torch.cat([out, model(idx[:, p : p + 1], torch.tensor([p], device="cuda"))], dim=1)
     assert out.shape == (2, 12, cfg["vocab"])
     assert rel_err(out[0], O.forward(cfg, w, a, torch.float64)) < 2e-5 and rel_err(out[1], O.forward(cfg, w, b, torch.float64)) < 2e-5
+
+
+def _write_checkpoint(folder, cfg, weights):
+    import json
+    import struct
+
+    header, blob = {}, b""
+    for name, t in weights.items():
+        raw = t.contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [len(blob), len(blob) + len(raw)]}
+        blob += raw
+    hj = json.dumps(header).encode()
+    (folder / "model.safetensors").write_bytes(struct.pack("<Q", len(hj)) + hj + blob)
+    (folder / "config.json").write_text(json.dumps(cfg))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_runner_end_to_end(tmp_path, dtype):
+    """The command-line replayer on a checkpoint directory written here: a ragged first step, decoding together, a request that
+    ends, a new one in its slot, steps without anything wanted -- the files it writes against the oracle."""
+    import json
+    import subprocess
+
+    import numpy as np
+
+    cfg = CFG_ODD
+    w = checkpoint(cfg, 101)
+    _write_checkpoint(tmp_path, cfg, w)
+    a, b, c = tokens_for(cfg, 40, 102), tokens_for(cfg, 9, 103), tokens_for(cfg, 70, 104)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:37], "want": [0, 36]}, {"id": "b", "tokens": b[:6], "want": [5]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": [a[37]], "want": []}, {"id": "b", "tokens": [b[6]], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": [a[38]], "want": [0]}, {"id": "b", "tokens": [b[7]], "want": [0]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": [a[39]], "want": [0]}], "end": ["a"]},
+        {"step": 4, "entries": [{"id": "c", "tokens": c, "want": [0, 1, 63, 64, 69]}], "end": ["c"]},
+    ]
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", dtype, "--out", str(out), "--max-tokens", "120"],
+                         input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert [l for l in res.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+    assert sorted(os.listdir(out)) == ["0.f32", "2.f32", "3.f32", "4.f32"]        # step 1 wanted nothing
+    full = {k: O.forward(cfg, w, t, torch.float64) for k, t in (("a", a), ("b", b), ("c", c))}
+    want = {0: torch.stack([full["a"][0], full["a"][36], full["b"][5]]), 2: torch.stack([full["a"][38], full["b"][7]]),
+            3: full["a"][39:40], 4: full["c"][[0, 1, 63, 64, 69]]}
+    dt = torch.float32 if dtype == "float32" else torch.bfloat16
+    for step, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, cfg["vocab"]))
+        assert got.shape == ref.shape
+        assert_close(got, ref, dt, f"step {step}") if dt == torch.float32 else assert_close(torch.cat([got] * 4), torch.cat([ref] * 4), dt, f"step {step}")
