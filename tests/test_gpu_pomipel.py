@@ -185,7 +185,7 @@ def test_embedding_with_positions(dtype):
     assert rel_err(x, want) < 1e-6 and torch.equal(act, x.to(dtype))
 
 
-@pytest.mark.parametrize("experts,top,groups,keep", [(16, 3, 2, 1), (12, 4, 4, 2), (6, 1, 1, 1), (8, 2, 8, 3), (9, 3, 3, 3)])
+@pytest.mark.parametrize("experts,top,groups,keep", [(18, 5, 2, 1), (12, 4, 4, 2), (6, 1, 1, 1), (8, 2, 8, 3), (9, 3, 3, 3)])
 def test_router(experts, top, groups, keep):
     k = K()
     g = torch.Generator().manual_seed(experts * 100 + top)
