@@ -422,10 +422,12 @@ int b200_latent_decode(const b200_latent_decode_args* args, b200_stream_t stream
 /* test knob: non-zero keeps bf16 decode on the any-size kernel instead of the tensor-core one; returns the previous setting */
 int b200_latent_decode_tune(int force_any_size_kernel);
 
-/* Router: s = sigmoid(W_router x); experts are chosen by s + correction among the `keep` best of `n_group` equal groups of
- * neighbours (group rank = sum of its two largest corrected scores); weights[t, k] = s of the chosen expert. */
+/* Router: s = sigmoid(W_router x), or softmax over all experts with B200_ROUTE_SOFTMAX; experts are chosen by s + correction among
+ * the `keep` best of `n_group` equal groups of neighbours (group rank = sum of its two largest corrected scores, or the largest
+ * with B200_ROUTE_GROUP_MAX); weights[t, k] = s of the chosen expert, not renormalised. */
+enum b200_route_flags { B200_ROUTE_SOFTMAX = 1, B200_ROUTE_GROUP_MAX = 2 };
 int b200_moe_route(const void* x, const void* w_router, const void* correction, int32_t* ids, float* weights, int64_t tokens, int d,
-                   int n_expert, int top, int n_group, int keep, int dtype, b200_stream_t stream);
+                   int n_expert, int top, int n_group, int keep, int flags, int dtype, b200_stream_t stream);
 /* counting sort of the (token, choice) pairs by expert: expert_off[E + 1], tile_off[E + 1] (64-row tiles), slot_token[tokens * top],
  * slot_of[tokens * top] */
 int b200_moe_plan(const int32_t* ids, int64_t tokens, int top, int n_expert, int32_t* expert_off, int32_t* tile_off, int32_t* slot_token,
@@ -433,11 +435,96 @@ int b200_moe_plan(const int32_t* ids, int64_t tokens, int top, int n_expert, int
 /* c[row, :n] = act(a[row_src ? row_src[row] : row, :k] . w[e][:n, :k]^T) for the rows of every expert e; act = relu^2 or none */
 int b200_moe_gemm(const void* a, int64_t lda, const int32_t* row_src, const void* w, void* c, int64_t ldc, const int32_t* expert_off,
                   const int32_t* tile_off, int64_t rows, int n_expert, int n, int k, int sqrelu, int dtype, b200_stream_t stream);
-/* few tokens: hidden = relu(W_up[e] x)^2 per (token, choice), out[t] = sum_k weights[t, k] * W_down[e_k] hidden[t, k] */
+/* few tokens: hidden = relu(W_up[e] x)^2 per (token, choice) -- gated: silu(W_up[e][:ff] x) * (W_up[e][ff:] x) with 2 ff rows per
+ * expert --, out[t] = sum_k weights[t, k] * W_down[e_k] hidden[t, k] */
 int b200_moe_gemv(const void* x, const int32_t* ids, const float* weights, const void* w_up, const void* w_down, void* hidden, void* out,
-                  int64_t tokens, int top, int d, int ff, int dtype, b200_stream_t stream);
+                  int64_t tokens, int top, int d, int ff, int gated, int dtype, b200_stream_t stream);
 int b200_moe_combine(const void* y, const int32_t* slot_of, const float* weights, void* out, int64_t tokens, int top, int d, int dtype,
                      b200_stream_t stream);
+
+/* ---- sequence-state mechanisms: short convolutions, the gated delta rule, windowed attention over a ring -------------------
+ * A step's rows are the new tokens of several sequences packed one after another; seqs[s] = {first row, rows, position of the
+ * first row, state slot} (int32[n_seqs][4], 16-byte aligned) and row_seq[row] = s. */
+
+/* x += norm(y) * post_w [+ extra]; act = dtype(norm(x) * pre_w), with y = y0 or the mean of norm(y0) * w0 and norm(y1) * w1;
+ * norm(z) = z / sqrt(mean(z^2) + eps).  post_w NULL: y joins as it is; pre_w NULL: act is not written. */
+typedef struct b200_sandwich_args {
+  const void* y0; const void* w0; const void* y1; const void* w1;
+  const void* post_w; const float* extra; const void* pre_w;
+  float* x; void* act;
+  int64_t rows; int d; float eps; int dtype;
+} b200_sandwich_args;
+int b200_sandwich_residual(const b200_sandwich_args* args, b200_stream_t stream);
+/* in place; kind 0 exact gelu (erf), 1 tanh gelu, 2 silu, 3 relu^2 */
+int b200_activation(void* x, int64_t n, int kind, int dtype, b200_stream_t stream);
+/* out[r, c] = act(in[r, c]) * in[r, ff + c] for in (rows, 2 ff) */
+int b200_glu(const void* in, void* out, int64_t rows, int ff, int kind, int dtype, b200_stream_t stream);
+
+/* One group of heads of a short causal convolution (see b200_short_conv). */
+typedef struct b200_conv_group {
+  const void* w;            /* (heads * dim, taps), model dtype; the last column multiplies the current token */
+  void* out;                /* (rows, heads * dim) with leading dimension ld_out; fp32 when out_f32, else model dtype */
+  int64_t ld_out;
+  const double* inv_freq;   /* rot_dims / 2 angular frequencies (post = 1) */
+  int col0;                 /* first column of the group in the input rows and in the tail */
+  int heads, dim;
+  int act;                  /* 0 none, 1 silu */
+  int post;                 /* 0 none, 1 rotate then x / sqrt(mean(x^2) + eps), 2 x / sqrt(sum(x^2) + eps) */
+  int rot_dims;
+  int out_f32;
+  float rot_mscale;         /* multiplies cos and sin */
+  float post_scale;         /* multiplies the result */
+  float eps;
+} b200_conv_group;
+/* y[t, c] = sum_j w[c, j] * in[t - taps + 1 + j, c] per sequence (zeros before position 0; rows before the step from tail
+ * (slots, taps - 1, tail_cols)), then act and post per head.  in (rows, >= tail_cols) with leading dimension ld_in. */
+int b200_short_conv(const void* in, int64_t ld_in, const b200_conv_group* groups, int n_groups, int taps, const void* tail,
+                    int64_t tail_slot_stride, int tail_cols, const int32_t* seqs, const int32_t* row_seq, int64_t rows, int dtype,
+                    b200_stream_t stream);
+/* tail[slot] <- the last taps - 1 input rows of every sequence after this step (call after b200_short_conv) */
+int b200_conv_tail_update(const void* in, int64_t ld_in, void* tail, int64_t tail_slot_stride, int tail_cols, int taps, const int32_t* seqs,
+                          int n_seqs, int dtype, b200_stream_t stream);
+
+/* Gated delta rule over fp32 states, one dk x dv matrix per (slot, head): per token S *= g; u = beta (v - S^T k); S += k u^T;
+ * o = S^T q, with beta = sigmoid(beta_in) and g = exp(-exp(a_log) * softplus(decay_in + dt_bias)); decay_in and dt_bias hold one
+ * number per head, or per head and key channel with channel_decay.  q, k (rows, kv_heads * dk), v (rows, heads * dv) and out are
+ * fp32; the raw projections and parameters are in the model dtype.  A sequence at position 0 starts from S = 0. */
+typedef struct b200_delta_rule_args {
+  const float* q; const float* k; const float* v;
+  int64_t ldq, ldk, ldv;
+  const void* beta_in; int64_t ld_beta;
+  const void* decay_in; int64_t ld_decay;
+  const void* a_log; const void* dt_bias;
+  float* state; int64_t state_slot_stride;   /* floats per slot: heads * b200_delta_rule_state_floats(dk, dv) or more */
+  float* out; int64_t ldo;
+  const int32_t* seqs; int n_seqs;
+  int heads, kv_heads, dk, dv, channel_decay, dtype;
+} b200_delta_rule_args;
+int64_t b200_delta_rule_state_floats(int dk, int dv);
+int b200_delta_rule(const b200_delta_rule_args* args, b200_stream_t stream);
+/* out[row, h, :] = dtype(o / sqrt(mean(o^2) + eps) * weight * gate(z)) per head; gate 1 silu, 2 sigmoid */
+int b200_gated_rms_heads(const float* o, int64_t ldo, const void* z, int64_t ldz, const void* weight, void* out, int64_t ld_out, int64_t rows,
+                         int heads, int dv, int gate, float eps, int dtype, b200_stream_t stream);
+
+/* Sliding-window attention with a per-head sink logit in the softmax denominator (sink NULL: none).  Row at position i sees
+ * positions i - window < j <= i: those of this step from k / v (rows, n_kv_head * dk | dv), older ones from the rings
+ * (slots, ring, n_kv_head * dk | dv) where position p sits in row p % ring. */
+typedef struct b200_window_attn_args {
+  const void* q; const void* k; const void* v; void* out;
+  int64_t ldq, ldk, ldv, ldo;
+  const void* k_ring; const void* v_ring;
+  const void* sink;
+  const int32_t* seqs;
+  int n_seqs, max_q_len, ring, n_head, n_kv_head, dk, dv, window;
+  float scale;
+  int dtype;
+} b200_window_attn_args;
+int b200_window_attn(const b200_window_attn_args* args, b200_stream_t stream);
+/* test knob: non-zero keeps single-row steps on the tiled kernel; returns the previous setting */
+int b200_window_attn_tune(int force_tiled_kernel);
+/* the step's rows among each sequence's last `ring` positions go to their ring rows (call after b200_window_attn) */
+int b200_ring_store(const void* k, int64_t ldk, const void* v, int64_t ldv, void* k_ring, void* v_ring, int ring, int kcols, int vcols,
+                    const int32_t* seqs, const int32_t* row_seq, int64_t rows, int dtype, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -93,9 +93,38 @@ class LatentDecodeArgs(ctypes.Structure):  # mirrors b200_latent_decode_args
                 ("scale", c_float), ("dtype", c_int), ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
 
 
+class SandwichArgs(ctypes.Structure):  # mirrors b200_sandwich_args
+    _fields_ = [("y0", c_void_p), ("w0", c_void_p), ("y1", c_void_p), ("w1", c_void_p), ("post_w", c_void_p), ("extra", c_void_p),
+                ("pre_w", c_void_p), ("x", c_void_p), ("act", c_void_p), ("rows", c_int64), ("d", c_int), ("eps", c_float), ("dtype", c_int)]
+
+
+class ConvGroup(ctypes.Structure):  # mirrors b200_conv_group
+    _fields_ = [("w", c_void_p), ("out", c_void_p), ("ld_out", c_int64), ("inv_freq", c_void_p), ("col0", c_int), ("heads", c_int), ("dim", c_int),
+                ("act", c_int), ("post", c_int), ("rot_dims", c_int), ("out_f32", c_int), ("rot_mscale", c_float), ("post_scale", c_float),
+                ("eps", c_float)]
+
+
+class DeltaRuleArgs(ctypes.Structure):  # mirrors b200_delta_rule_args
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("ldq", c_int64), ("ldk", c_int64), ("ldv", c_int64),
+                ("beta_in", c_void_p), ("ld_beta", c_int64), ("decay_in", c_void_p), ("ld_decay", c_int64), ("a_log", c_void_p),
+                ("dt_bias", c_void_p), ("state", c_void_p), ("state_slot_stride", c_int64), ("out", c_void_p), ("ldo", c_int64),
+                ("seqs", c_void_p), ("n_seqs", c_int), ("heads", c_int), ("kv_heads", c_int), ("dk", c_int), ("dv", c_int),
+                ("channel_decay", c_int), ("dtype", c_int)]
+
+
+class WindowAttnArgs(ctypes.Structure):  # mirrors b200_window_attn_args
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p), ("ldq", c_int64), ("ldk", c_int64), ("ldv", c_int64),
+                ("ldo", c_int64), ("k_ring", c_void_p), ("v_ring", c_void_p), ("sink", c_void_p), ("seqs", c_void_p), ("n_seqs", c_int),
+                ("max_q_len", c_int), ("ring", c_int), ("n_head", c_int), ("n_kv_head", c_int), ("dk", c_int), ("dv", c_int), ("window", c_int),
+                ("scale", c_float), ("dtype", c_int)]
+
+
+ROUTE_SOFTMAX, ROUTE_GROUP_MAX = 1, 2
+ACT_GELU, ACT_GELU_TANH, ACT_SILU, ACT_RELU2 = 0, 1, 2, 3
+
 # Entry points of the sources every model needs (library state, norms, sampling) and of the fp32-residual / latent-attention /
 # expert kernels: `load_core()` can serve them from a library built from those sources alone.
-_CORE_SOURCES = ("api.cu", "norm.cu", "sample.cu", "resid.cu", "latent.cu", "moe.cu", "attn_prefill.cu")
+_CORE_SOURCES = ("api.cu", "norm.cu", "sample.cu", "resid.cu", "latent.cu", "moe.cu", "attn_prefill.cu", "shortconv.cu", "delta.cu", "window_attn.cu")
 _CORE_SIGNATURES = {
     "b200_embed_pos": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_rms_rows": (c_int, [ctypes.POINTER(RmsRowsSeg), c_int, c_int64, c_float, c_int, c_int, c_void_p]),
@@ -109,12 +138,26 @@ _CORE_SIGNATURES = {
     "b200_latent_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200_latent_decode": (c_int, [ctypes.POINTER(LatentDecodeArgs), c_void_p]),
     "b200_latent_decode_tune": (c_int, [c_int]),
-    "b200_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_moe_plan": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_moe_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                               c_void_p]),
-    "b200_moe_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_moe_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_sandwich_residual": (c_int, [ctypes.POINTER(SandwichArgs), c_void_p]),
+    "b200_activation": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "b200_glu": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_short_conv": (c_int, [c_void_p, c_int64, ctypes.POINTER(ConvGroup), c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int,
+                                c_void_p]),
+    "b200_conv_tail_update": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "b200_delta_rule_state_floats": (c_int64, [c_int, c_int]),
+    "b200_delta_rule": (c_int, [ctypes.POINTER(DeltaRuleArgs), c_void_p]),
+    "b200_gated_rms_heads": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_float, c_int,
+                                     c_void_p]),
+    "b200_window_attn": (c_int, [ctypes.POINTER(WindowAttnArgs), c_void_p]),
+    "b200_window_attn_tune": (c_int, [c_int]),
+    "b200_ring_store": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_int,
+                                c_void_p]),
 }
 _CORE_SHARED = ("b200_abi_version", "b200_last_error", "b200_device_info", "b200_set_pdl", "b200_launch_count", "b200_rmsnorm", "b200_swiglu",
                 "b200_embedding", "b200_argmax", "b200_sample", "b200_attn_prefill")

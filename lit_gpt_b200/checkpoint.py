@@ -120,3 +120,26 @@ def read_safetensors(path: Union[str, os.PathLike]) -> Dict[str, torch.Tensor]:
             raise B200Error(f"{path}: tensor {name!r} has inconsistent offsets")
         out[name] = (torch.frombuffer(bytearray(data[lo:hi]), dtype=dtype).reshape(shape) if count else torch.empty(shape, dtype=dtype))
     return out
+
+
+def load_registered(checkpoint_dir: Union[str, os.PathLike], dtype: torch.dtype = torch.bfloat16, device: Any = "cuda") -> nn.Module:
+    """Build the model a checkpoint directory (``config.json`` naming a registered architecture + ``model.safetensors``)
+    describes, on `device` in `dtype`.  A model class may complete its configuration from the tensors' shapes
+    (``complete_config``) before it is built."""
+    from pathlib import Path
+
+    from .config import Config, load_config, model_class
+
+    path = Path(checkpoint_dir)
+    config = load_config(path)
+    if isinstance(config, Config):
+        raise TypeError(f"{str(path)!r} holds a flat lit_config.json: load it through Fabric and GPT")
+    cls = model_class(config)
+    tensors = {k: v for k, v in read_safetensors(path / "model.safetensors").items() if v.is_floating_point()}
+    if hasattr(cls, "complete_config"):
+        cls.complete_config(config, {k: tuple(v.shape) for k, v in tensors.items()})
+    with torch.device("meta"):
+        model = cls(config)
+    model = model.to_empty(device=device).to(dtype)
+    model.load_tensors(tensors)
+    return model.eval()

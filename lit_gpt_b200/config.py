@@ -11,7 +11,7 @@ from __future__ import annotations
 import json
 from dataclasses import dataclass, field
 from pathlib import Path
-from typing import Any, Dict, List, Literal, Optional, Type, Union
+from typing import Any, Dict, List, Literal, Optional, Tuple, Type, Union
 
 import torch
 
@@ -275,8 +275,209 @@ class PomipelConfig:
             return cls.from_dict(json.load(fp))
 
 
+@dataclass
+class RotarySpec:
+    """Rotary positions on the first `dims` dimensions of a head, interleaved pairs (2i, 2i + 1), frequency base^(-2i / dims);
+    with `factor` set the frequencies are blended towards f / factor over a ramp between the dimensions whose wavelength
+    fits `fast` and `slow` times into `original` positions (YaRN), and cos / sin are scaled by 0.1 ln(factor) + 1."""
+
+    dims: int
+    base: float
+    factor: Optional[float] = None
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
+
+    def frequencies(self) -> List[float]:
+        """Angular frequency of every pair, as Python floats (double precision)."""
+        import math
+
+        half = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
+        if self.factor is None:
+            return f
+
+        def pair_of(turns: float) -> float:   # the (fractional) pair index whose wavelength makes `turns` turns over `original`
+            return self.dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+        lo = max(math.floor(pair_of(self.fast)), 0)
+        hi = min(math.ceil(pair_of(self.slow)), self.dims - 1)
+        out = []
+        for i, fi in enumerate(f):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(fi / self.factor * ramp + fi * (1.0 - ramp))
+        return out
+
+    @property
+    def magnitude(self) -> float:
+        import math
+
+        return 1.0 if self.factor is None else 0.1 * math.log(self.factor) + 1.0
+
+
+@dataclass
+class WindowMixerSpec:
+    """Sliding-window attention with a sink: biased projections, a short convolution on q, k and v, rotary positions and a
+    weightless per-head RMS norm on q and k."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int                      # taps of the short convolution (1: none)
+    window: int                    # a position sees itself and the window - 1 before it
+    scale: float
+    rot: Optional[RotarySpec] = None
+
+
+@dataclass
+class DeltaMixerSpec:
+    """Gated delta rule: `heads` value heads of size vdim over `kv_heads` query / key heads of size dim; one decay per head, or
+    (`channel`) one per head and key channel through a low-rank projection, with a low-rank sigmoid output gate."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    channel: bool = False
+    decay_rank: int = 0            # inner size of the low-rank decay and gate projections (channel); read from the weights' shapes
+    gate_rank: int = 0
+
+
+@dataclass
+class ParallelMixerSpec:
+    left: WindowMixerSpec
+    right: DeltaMixerSpec
+
+
+@dataclass
+class DenseMLPSpec:
+    ff: int
+
+
+@dataclass
+class GatedMoESpec:
+    """Softmax router over all experts, group-limited choice (a group ranks by its largest score), weights = the chosen scores;
+    experts W_down (silu(W_gate h) * (W_up h))."""
+
+    experts: int
+    top: int
+    ff: int
+    groups: int = 1
+    keep: int = 1
+
+
+@dataclass
+class LefalixLayerSpec:
+    type: str                      # "parallel" | "channel_delta"
+    mixer: Any                     # ParallelMixerSpec | DeltaMixerSpec
+    mlp: Any = None                # DenseMLPSpec | GatedMoESpec | None
+
+
+@dataclass
+class LefalixConfig:
+    """Lefalix: blocks with RMS norms before and after each sublayer over an fp32 residual stream; mixers are a gated delta
+    rule with per-channel decay, or sliding-window attention and a gated delta rule side by side; feed-forwards dense (gelu)
+    or sparse gated experts.  Layers loop_start .. loop_stop - 1 run loop_times times with the same weights (each pass with
+    its own state), the embedding re-entering before every pass but the first."""
+
+    name: str = "Lefalix"
+    vocab_size: int = 0
+    n_embd: int = 0
+    norm_eps: float = 1e-5
+    layers: List[LefalixLayerSpec] = field(default_factory=list)
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    block_size: int = 1 << 30      # no position table and constant-size state: positions are bounded by int32 only
+
+    def __post_init__(self) -> None:
+        self.padded_vocab_size = self.vocab_size
+        self.n_layer = len(self.layers)
+        if self.loop_times < 1 or not 0 <= self.loop_start <= self.loop_stop <= self.n_layer:
+            raise ValueError(f"loop {self.loop_start}..{self.loop_stop} x {self.loop_times} does not fit {self.n_layer} layers")
+        for i, layer in enumerate(self.layers):
+            if layer.type not in ("parallel", "channel_delta"):
+                raise ValueError(f"layer {i}: unknown mixer type {layer.type!r}")
+            deltas = [layer.mixer.right] if layer.type == "parallel" else [layer.mixer]
+            if layer.type == "parallel":
+                w = layer.mixer.left
+                if w.heads % w.kv_heads or w.window < 1 or w.conv < 1:
+                    raise ValueError(f"layer {i}: bad window-attention shape")
+                if w.rot is not None and (w.rot.dims % 2 or w.rot.dims > w.dim):
+                    raise ValueError(f"layer {i}: rotary dimensions must be even and at most the head size")
+            for m in deltas:
+                if m.heads % m.kv_heads or m.conv < 1:
+                    raise ValueError(f"layer {i}: bad delta-rule shape")
+            m = layer.mlp
+            if isinstance(m, GatedMoESpec) and (m.experts % m.groups or not 0 < m.keep <= m.groups or m.keep * (m.experts // m.groups) < m.top):
+                raise ValueError(f"layer {i}: expert groups {m.groups} / keep {m.keep} do not fit {m.experts} experts, top {m.top}")
+
+    def schedule(self) -> List[Tuple[int, int, bool]]:
+        """The layer runs in order: (layer index, state index, first run of a repeated pass).  Every run has a state of its own."""
+        runs: List[Tuple[int, int, bool]] = []
+        order = [(i, False) for i in range(self.loop_start)]
+        for t in range(self.loop_times):
+            order += [(i, t > 0 and i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
+        order += [(i, False) for i in range(self.loop_stop, self.n_layer)]
+        for n, (i, reenter) in enumerate(order):
+            runs.append((i, n, reenter))
+        return runs
+
+    @staticmethod
+    def _delta(mx: Dict[str, Any], channel: bool) -> DeltaMixerSpec:
+        return DeltaMixerSpec(heads=int(mx["heads"]), kv_heads=int(mx["kv_heads"]), dim=int(mx["dim"]), vdim=int(mx["vdim"]),
+                              conv=int(mx.get("conv", 1)), channel=channel, decay_rank=int(mx.get("decay_rank", 0)),
+                              gate_rank=int(mx.get("gate_rank", 0)))
+
+    @classmethod
+    def from_dict(cls, js: Dict[str, Any]) -> "LefalixConfig":
+        layers = []
+        for i, entry in enumerate(js["layers"]):
+            mx, kind = entry["mixer"], entry["type"]
+            if kind == "parallel":
+                lf = mx["left"]
+                rot = None
+                if lf.get("rot") is not None:
+                    r = lf["rot"]
+                    sc = r.get("scaling")
+                    rot = RotarySpec(dims=int(r["dims"]), base=float(r["base"])) if sc is None else RotarySpec(
+                        dims=int(r["dims"]), base=float(r["base"]), factor=float(sc["factor"]), original=float(sc["original"]),
+                        fast=float(sc["fast"]), slow=float(sc["slow"]))
+                left = WindowMixerSpec(heads=int(lf["heads"]), kv_heads=int(lf["kv_heads"]), dim=int(lf["dim"]), vdim=int(lf["vdim"]),
+                                       conv=int(lf.get("conv", 1)), window=int(lf["mask"]["size"]), scale=float(lf["scale"]), rot=rot)
+                mixer: Any = ParallelMixerSpec(left=left, right=cls._delta(mx["right"], False))
+            elif kind == "channel_delta":
+                mixer = cls._delta(mx, True)
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            mlp: Any = None
+            if entry.get("mlp") is not None:
+                ml = entry["mlp"]
+                if ml.get("kind") == "dense":
+                    mlp = DenseMLPSpec(ff=int(ml["ff"]))
+                elif ml.get("kind") == "moe":
+                    router, groups = ml["router"], ml["router"].get("groups") or {}
+                    mlp = GatedMoESpec(experts=int(router["experts"]), top=int(router["top"]), ff=int(ml["expert"]["ff"]),
+                                       groups=int(groups.get("count", 1)), keep=int(groups.get("keep", groups.get("count", 1))))
+                else:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {ml.get('kind')!r}")
+            layers.append(LefalixLayerSpec(type=kind, mixer=mixer, mlp=mlp))
+        loop = js.get("loop") or {}
+        return cls(name=js.get("architecture", "Lefalix"), vocab_size=int(js["vocab"]), n_embd=int(js["width"]),
+                   norm_eps=float(js["norm"]["eps"]), layers=layers, loop_start=int(loop.get("start", 0)),
+                   loop_stop=int(loop.get("stop", loop.get("start", 0))), loop_times=int(loop.get("times", 1)))
+
+    @classmethod
+    def from_json(cls, path: Union[str, Path]) -> "LefalixConfig":
+        with open(path, encoding="utf-8") as fp:
+            return cls.from_dict(json.load(fp))
+
+
 # "architecture" value of config.json -> (configuration class, "module:class" of the model)
-architectures: Dict[str, Any] = {"Pomipel": (PomipelConfig, "lit_gpt_b200.pomipel:Pomipel")}
+architectures: Dict[str, Any] = {"Pomipel": (PomipelConfig, "lit_gpt_b200.pomipel:Pomipel"),
+                                 "Lefalix": (LefalixConfig, "lit_gpt_b200.lefalix:Lefalix")}
 
 
 def load_config(checkpoint_dir: Union[str, Path], **kwargs: Any) -> Any:

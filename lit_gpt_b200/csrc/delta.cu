@@ -1,0 +1,233 @@
+// Gated delta rule: a recurrent layer whose state is one dk x dv matrix S per head, kept in fp32.
+//
+//   per token:  S <- g * S          (g: one decay per head, or one per head and key channel acting on the rows of S)
+//               u  = beta * (v - S^T k)
+//               S <- S + k u^T
+//               o  = S^T q          (the read-out sees the token's own write)
+//   with beta = sigmoid(b) and g = exp(-exp(A_log) * softplus(a + dt_bias)) computed here in fp32 from the raw projections.
+//
+// The columns of S never mix: column j evolves from (k, q, g, beta) and v[j] alone.  So the work of one (sequence, head) is
+// split over columns -- a group of LPC lanes owns one column, each lane holding dk / LPC of its numbers in registers -- and
+// over CTAs (column blocks).  Time is walked in order: tiles of tokens are staged in shared memory (keys, queries, decays
+// already turned into g), then every lane group does two short dot products and two updates per token.  One kernel serves
+// prompts (many rows per sequence) and decoding (one row: the cost is reading and writing S once).
+//
+// A sequence that starts at position 0 starts from S = 0 whatever its slot holds.  The state is stored in the order the
+// lanes read it: element (key i, column j) of a head at ((i / LPC) * dv + j) * LPC + i % LPC, so that a warp moves 128
+// contiguous bytes per register.
+//
+// b200_gated_rms_heads is the step after the read-out: per head, o / sqrt(mean(o^2) + eps) * weight * gate(z) with
+// gate = silu or sigmoid.
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kDrThreads = 128, kDrKPL = 16;   // keys per lane (registers of state per thread)
+
+__host__ __device__ inline int delta_lpc(int dk) { return dk <= 64 ? 4 : dk <= 128 ? 8 : dk <= 256 ? 16 : 32; }
+__host__ __device__ inline int delta_key_rows(int dk) { const int l = delta_lpc(dk); return (dk + l - 1) / l; }
+
+struct DrArgs {
+  const float* q; const float* k; const float* v;
+  int64_t ldq, ldk, ldv;
+  const void* beta_in; int64_t ld_beta;
+  const void* decay_in; int64_t ld_decay;
+  const void* a_log; const void* dt_bias;
+  float* state; int64_t state_slot_stride;
+  float* out; int64_t ldo;
+  const int4* seqs;
+  int heads, kv_heads, dk, dv;
+};
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+template <typename T, int LPC, bool CHANNEL>
+__global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A) {
+  constexpr int TT = 64 / LPC;                 // tokens per staged tile
+  constexpr int DKP = kDrKPL * LPC;            // padded key size
+  constexpr int COLS = kDrThreads / LPC;       // columns per CTA
+  extern __shared__ __align__(16) float dr_smem[];
+  float* const ks = dr_smem;                   // [TT][DKP]
+  float* const qs = ks + TT * DKP;             // [TT][DKP]
+  float* const gs = qs + TT * DKP;             // [TT][DKP] (channel decay) or [TT]
+  float* const vs = gs + (CHANNEL ? TT * DKP : TT);   // [TT][COLS]
+  float* const bs = vs + TT * COLS;            // [TT]
+  griddep_launch();
+  griddep_wait();
+  const int tid = threadIdx.x, sub = tid % LPC, cl = tid / LPC;
+  const int h = blockIdx.y, hk = h / (A.heads / A.kv_heads);
+  const int4 sq = A.seqs[blockIdx.z];
+  const int first = sq.x, len = sq.y, pos0 = sq.z, slot = sq.w;
+  const int col = (int)blockIdx.x * COLS + cl;
+  const bool col_ok = col < A.dv;
+  const int dk = A.dk, dv = A.dv;
+  const int krows = (dk + LPC - 1) / LPC;
+  float* const st = A.state + (int64_t)slot * A.state_slot_stride + (int64_t)h * krows * LPC * dv;
+
+  float S[kDrKPL];
+#pragma unroll
+  for (int r = 0; r < kDrKPL; ++r) S[r] = (pos0 > 0 && col_ok && r < krows) ? st[((int64_t)r * dv + col) * LPC + sub] : 0.f;
+
+  const float neg_a = -expf(load_as_float(reinterpret_cast<const T*>(A.a_log), h));
+  const T* const bias = reinterpret_cast<const T*>(A.dt_bias);
+  const T* const dec = reinterpret_cast<const T*>(A.decay_in);
+  const T* const bet = reinterpret_cast<const T*>(A.beta_in);
+
+  for (int t0 = 0; t0 < len; t0 += TT) {
+    const int nt = min(TT, len - t0);
+    __syncthreads();
+    for (int idx = tid; idx < TT * DKP; idx += kDrThreads) {
+      const int t = idx / DKP, i = idx - t * DKP;
+      float kv = 0.f, qv = 0.f, gv = 1.f;
+      if (t < nt && i < dk) {
+        const int64_t row = first + t0 + t;
+        kv = A.k[row * A.ldk + (int64_t)hk * dk + i];
+        qv = A.q[row * A.ldq + (int64_t)hk * dk + i];
+        if (CHANNEL) gv = expf(neg_a * softplus_f(load_as_float(dec, row * A.ld_decay + (int64_t)h * dk + i) + load_as_float(bias, (int64_t)h * dk + i)));
+      }
+      ks[idx] = kv;
+      qs[idx] = qv;
+      if (CHANNEL) gs[idx] = gv;
+    }
+    for (int idx = tid; idx < TT * COLS; idx += kDrThreads) {
+      const int t = idx / COLS, c = (int)blockIdx.x * COLS + (idx - t * COLS);
+      vs[idx] = (t < nt && c < dv) ? A.v[(int64_t)(first + t0 + t) * A.ldv + (int64_t)h * dv + c] : 0.f;
+    }
+    if (tid < TT) {
+      float b = 0.f, g = 1.f;
+      if (tid < nt) {
+        const int64_t row = first + t0 + tid;
+        b = 1.0f / (1.0f + expf(-load_as_float(bet, row * A.ld_beta + h)));
+        if (!CHANNEL) g = expf(neg_a * softplus_f(load_as_float(dec, row * A.ld_decay + h) + load_as_float(bias, h)));
+      }
+      bs[tid] = b;
+      if (!CHANNEL) gs[tid] = g;
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float* kt = ks + t * DKP + sub;
+      const float* qt = qs + t * DKP + sub;
+      float kr[kDrKPL];
+      float dot = 0.f;
+      if (CHANNEL) {
+        const float* gt = gs + t * DKP + sub;
+#pragma unroll
+        for (int r = 0; r < kDrKPL; ++r) {
+          kr[r] = kt[r * LPC];
+          S[r] *= gt[r * LPC];
+          dot = fmaf(S[r], kr[r], dot);
+        }
+      } else {
+        const float g = gs[t];
+#pragma unroll
+        for (int r = 0; r < kDrKPL; ++r) {
+          kr[r] = kt[r * LPC];
+          S[r] *= g;
+          dot = fmaf(S[r], kr[r], dot);
+        }
+      }
+#pragma unroll
+      for (int o = LPC / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = bs[t] * (vs[t * COLS + cl] - dot);
+      float od = 0.f;
+#pragma unroll
+      for (int r = 0; r < kDrKPL; ++r) {
+        S[r] = fmaf(kr[r], u, S[r]);
+        od = fmaf(S[r], qt[r * LPC], od);
+      }
+#pragma unroll
+      for (int o = LPC / 2; o > 0; o >>= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
+      if (sub == 0 && col_ok) A.out[(int64_t)(first + t0 + t) * A.ldo + (int64_t)h * dv + col] = od;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int r = 0; r < kDrKPL; ++r)
+      if (r < krows) st[((int64_t)r * dv + col) * LPC + sub] = S[r];
+  }
+}
+
+template <typename T, int LPC>
+cudaError_t delta_launch(const DrArgs& A, bool channel, int n_seqs, cudaStream_t st) {
+  constexpr int TT = 64 / LPC, DKP = kDrKPL * LPC, COLS = kDrThreads / LPC;
+  const dim3 grid((unsigned)((A.dv + COLS - 1) / COLS), (unsigned)A.heads, (unsigned)n_seqs);
+  if (channel) {
+    const size_t smem = (size_t)(3 * TT * DKP + TT * COLS + TT) * sizeof(float);
+    static PerDeviceOnce once;
+    if (smem > 48 * 1024 && once.need()) {
+      cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<T, LPC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      once.done();
+    }
+    return launch(delta_rule_kernel<T, LPC, true>, grid, dim3(kDrThreads), smem, st, A);
+  }
+  const size_t smem = (size_t)(2 * TT * DKP + TT + TT * COLS + TT) * sizeof(float);
+  return launch(delta_rule_kernel<T, LPC, false>, grid, dim3(kDrThreads), smem, st, A);
+}
+
+// out[row, h, :] = T( o / sqrt(mean(o^2) + eps) * weight * gate(z[row, h, :]) ); one warp per (row, head)
+template <typename T>
+__global__ void __launch_bounds__(128) gated_rms_heads_kernel(const float* __restrict__ o, int64_t ldo, const T* __restrict__ z, int64_t ldz,
+                                                              const T* __restrict__ weight, T* __restrict__ out, int64_t ld_out, int heads,
+                                                              int dv, int gate, float eps) {
+  griddep_launch();
+  griddep_wait();
+  const int lane = threadIdx.x & 31;
+  const int h = (int)blockIdx.y * 4 + (threadIdx.x >> 5);
+  if (h >= heads) return;
+  const int64_t row = blockIdx.x;
+  const float* orow = o + row * ldo + (int64_t)h * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss = fmaf(orow[i], orow[i], ss);
+  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+  for (int i = lane; i < dv; i += 32) {
+    const float zz = load_as_float(z, row * ldz + (int64_t)h * dv + i);
+    const float sg = 1.0f / (1.0f + expf(-zz));
+    store_from_float(out, row * ld_out + (int64_t)h * dv + i, orow[i] * rstd * load_as_float(weight, i) * (gate == 1 ? zz * sg : sg));
+  }
+}
+
+}  // namespace
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int64_t b200_delta_rule_state_floats(int dk, int dv) { return (int64_t)delta_key_rows(dk) * delta_lpc(dk) * dv; }
+
+int b200_delta_rule(const b200_delta_rule_args* a, b200_stream_t stream) {
+  B200_CHECK_ARG(a && a->q && a->k && a->v && a->beta_in && a->decay_in && a->a_log && a->dt_bias && a->state && a->out && a->seqs,
+                 "b200_delta_rule: null pointer");
+  B200_CHECK_ARG(a->n_seqs > 0 && a->n_seqs <= 65535 && a->heads > 0 && a->heads <= 65535 && a->kv_heads > 0 && a->heads % a->kv_heads == 0,
+                 "b200_delta_rule: bad head counts");
+  B200_CHECK_ARG(a->dk > 0 && a->dk <= kDrKPL * 32 && a->dv > 0, "b200_delta_rule: key size must be 1 .. %d", kDrKPL * 32);
+  B200_CHECK_ARG((reinterpret_cast<uintptr_t>(a->seqs) & 15) == 0, "b200_delta_rule: seqs must be 16-byte aligned");
+  const DrArgs A{a->q, a->k, a->v, a->ldq, a->ldk, a->ldv, a->beta_in, a->ld_beta, a->decay_in, a->ld_decay, a->a_log, a->dt_bias,
+                 a->state, a->state_slot_stride, a->out, a->ldo, reinterpret_cast<const int4*>(a->seqs), a->heads, a->kv_heads, a->dk, a->dv};
+  const bool ch = a->channel_decay != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int lpc = delta_lpc(a->dk);
+  B200_FLOAT_TYPES(a->dtype, T, {
+    if (lpc == 4) B200_CUDA((delta_launch<T, 4>(A, ch, a->n_seqs, st)));
+    else if (lpc == 8) B200_CUDA((delta_launch<T, 8>(A, ch, a->n_seqs, st)));
+    else if (lpc == 16) B200_CUDA((delta_launch<T, 16>(A, ch, a->n_seqs, st)));
+    else B200_CUDA((delta_launch<T, 32>(A, ch, a->n_seqs, st)));
+  });
+  return B200_OK;
+}
+
+int b200_gated_rms_heads(const float* o, int64_t ldo, const void* z, int64_t ldz, const void* weight, void* out, int64_t ld_out, int64_t rows,
+                         int heads, int dv, int gate, float eps, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(o && z && weight && out, "b200_gated_rms_heads: null pointer");
+  B200_CHECK_ARG(rows > 0 && rows <= 0x7fffffff && heads > 0 && (heads + 3) / 4 <= 65535 && dv > 0, "b200_gated_rms_heads: bad shape");
+  B200_CHECK_ARG(gate == 1 || gate == 2, "b200_gated_rms_heads: gate is 1 (silu) or 2 (sigmoid)");
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(gated_rms_heads_kernel<T>, dim3((unsigned)rows, (unsigned)((heads + 3) / 4)), dim3(128), 0,
+                                               (cudaStream_t)stream, o, ldo, (const T*)z, ldz, (const T*)weight, (T*)out, ld_out, heads, dv, gate, eps)));
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,7 +1,8 @@
-// Sparse mixture of experts: a sigmoid router with a selection bias and group-limited choice, and the expert
-// feed-forward y = W_down act(W_up x) over stacked expert weights (E, ff, d) / (E, d, ff), act = relu(z)^2.
+// Sparse mixture of experts: a router (sigmoid or softmax scores, optional selection bias, group-limited choice) and the
+// expert feed-forward over stacked expert weights: y = W_down relu(W_up x)^2 with W_up (E, ff, d), or the gated form
+// y = W_down (silu(W_gate x) * (W_up x)) with the gate and up rows stacked as (E, 2 ff, d); W_down (E, d, ff).
 //
-//  * b200_moe_route: logits, sigmoid, choice and weights in fp32, one CTA per token.
+//  * b200_moe_route: logits, scores, choice and weights in fp32, one CTA per token.
 //  * b200_moe_plan: counting sort of the (token, choice) pairs by expert -> contiguous row ranges per expert.
 //  * b200_moe_gemm: grouped matrix product over those ranges (one launch for all experts, no host round trip), any
 //    sizes, bf16 or fp32 operands, fp32 accumulation; optional gather of the input rows and relu^2 epilogue.
@@ -37,7 +38,7 @@ template <typename T>
 __global__ void __launch_bounds__(kRtThreads) moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w_router,
                                                                 const T* __restrict__ correction, int* __restrict__ ids,
                                                                 float* __restrict__ wts, int d, int n_expert, int top, int n_group,
-                                                                int keep) {
+                                                                int keep, int flags) {
   extern __shared__ float rt_smem[];
   griddep_launch();
   griddep_wait();
@@ -50,20 +51,36 @@ __global__ void __launch_bounds__(kRtThreads) moe_route_kernel(const T* __restri
   for (int e = warp; e < n_expert; e += kRtThreads / 32) {
     const float z = warp_dot(xr, w_router + (int64_t)e * d, d, lane);
     if (lane == 0) {
-      const float s = 1.0f / (1.0f + expf(-z));
+      const float s = (flags & B200_ROUTE_SOFTMAX) ? z : 1.0f / (1.0f + expf(-z));
       score[e] = s;
       choice[e] = s + (correction ? load_as_float(correction, e) : 0.f);
     }
   }
   __syncthreads();
+  if (flags & B200_ROUTE_SOFTMAX) {   // scores = softmax over ALL experts, before any group is excluded
+    if (warp == 0) {
+      float mx = -INFINITY;
+      for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, score[e]);
+      mx = warp_max(mx);
+      float sum = 0.f;
+      for (int e = lane; e < n_expert; e += 32) sum += expf(score[e] - mx);
+      sum = warp_sum(sum);
+      for (int e = lane; e < n_expert; e += 32) {
+        const float s = expf(score[e] - mx) / sum;
+        score[e] = s;
+        choice[e] = s + (correction ? load_as_float(correction, e) : 0.f);
+      }
+    }
+    __syncthreads();
+  }
   const int per = n_expert / n_group;
-  for (int g = tid; g < n_group; g += kRtThreads) {   // a group's rank: the sum of its two largest choice scores
+  for (int g = tid; g < n_group; g += kRtThreads) {   // a group's rank: the sum of its two largest choice scores, or the largest
     float a = -INFINITY, b = -INFINITY;
     for (int i = 0; i < per; ++i) {
       const float c = choice[g * per + i];
       if (c > a) { b = a; a = c; } else if (c > b) { b = c; }
     }
-    grank[g] = per > 1 ? a + b : a;
+    grank[g] = (per > 1 && !(flags & B200_ROUTE_GROUP_MAX)) ? a + b : a;
   }
   __syncthreads();
   if (warp != 0) return;
@@ -204,8 +221,9 @@ __global__ void __launch_bounds__(kGmThreads) moe_gemm_kernel(const T* __restric
   }
 }
 
-// decode: hidden[p, f] = relu(W_up[ids[p]][f, :] . x[p / top, :])^2 for the pair p = t * top + k; one warp per f
-template <typename T>
+// decode: hidden[p, f] = relu(W_up[ids[p]][f, :] . x[p / top, :])^2 for the pair p = t * top + k; one warp per f.
+// GATED: W_up holds 2 ff rows per expert and hidden[p, f] = silu(row f . x) * (row ff + f . x).
+template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_gemv_up_kernel(const T* __restrict__ x, const int* __restrict__ ids, const T* __restrict__ w_up,
                                                           T* __restrict__ hidden, int top, int d, int ff) {
   griddep_launch();
@@ -214,6 +232,18 @@ __global__ void __launch_bounds__(256) moe_gemv_up_kernel(const T* __restrict__ 
   const int f = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (f >= ff) return;
   const T* xr = x + (int64_t)(p / top) * d;
+  if (GATED) {
+    const T* wg = w_up + ((int64_t)ids[p] * 2 * ff + f) * d;
+    const float gate = warp_dot(wg, xr, d, lane), up = warp_dot(wg + (int64_t)ff * d, xr, d, lane);
+    if (lane == 0) {   // both products take the matrix-product dtype before the activation, as in the grouped path
+      T gr, ur;
+      store_from_float(&gr, 0, gate);
+      store_from_float(&ur, 0, up);
+      const float gz = load_as_float(&gr, 0);
+      store_from_float(hidden, (int64_t)p * ff + f, gz / (1.0f + expf(-gz)) * load_as_float(&ur, 0));
+    }
+    return;
+  }
   const T* wr = w_up + ((int64_t)ids[p] * ff + f) * d;
   float acc = warp_dot(wr, xr, d, lane);
   if (lane == 0) {
@@ -281,7 +311,7 @@ using namespace b200;
 extern "C" {
 
 int b200_moe_route(const void* x, const void* w_router, const void* correction, int32_t* ids, float* weights, int64_t tokens, int d,
-                   int n_expert, int top, int n_group, int keep, int dtype, b200_stream_t stream) {
+                   int n_expert, int top, int n_group, int keep, int flags, int dtype, b200_stream_t stream) {
   B200_CHECK_ARG(x && w_router && ids && weights, "b200_moe_route: null pointer");
   B200_CHECK_ARG(tokens > 0 && tokens <= 0x7fffffff && d > 0 && n_expert > 0 && top > 0 && top <= n_expert, "b200_moe_route: bad shape");
   B200_CHECK_ARG(n_group > 0 && n_expert % n_group == 0 && keep > 0 && keep <= n_group, "b200_moe_route: groups must divide the experts");
@@ -289,7 +319,7 @@ int b200_moe_route(const void* x, const void* w_router, const void* correction, 
   const size_t smem = (size_t)(2 * n_expert + n_group) * sizeof(float);
   B200_CHECK_ARG(smem <= 48 * 1024, "b200_moe_route: too many experts");
   B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(moe_route_kernel<T>, dim3((unsigned)tokens), dim3(kRtThreads), smem, (cudaStream_t)stream, (const T*)x,
-                                               (const T*)w_router, (const T*)correction, ids, weights, d, n_expert, top, n_group, keep)));
+                                               (const T*)w_router, (const T*)correction, ids, weights, d, n_expert, top, n_group, keep, flags)));
   return B200_OK;
 }
 
@@ -320,13 +350,17 @@ int b200_moe_gemm(const void* a, int64_t lda, const int32_t* row_src, const void
 }
 
 int b200_moe_gemv(const void* x, const int32_t* ids, const float* weights, const void* w_up, const void* w_down, void* hidden, void* out,
-                  int64_t tokens, int top, int d, int ff, int dtype, b200_stream_t stream) {
+                  int64_t tokens, int top, int d, int ff, int gated, int dtype, b200_stream_t stream) {
   B200_CHECK_ARG(x && ids && weights && w_up && w_down && hidden && out, "b200_moe_gemv: null pointer");
   B200_CHECK_ARG(tokens > 0 && tokens * top <= 65535 && d > 0 && ff > 0, "b200_moe_gemv: bad shape");
   cudaStream_t st = (cudaStream_t)stream;
   B200_FLOAT_TYPES(dtype, T, {
-    B200_CUDA(launch(moe_gemv_up_kernel<T>, dim3((unsigned)((ff + 7) / 8), (unsigned)(tokens * top)), dim3(256), 0, st, (const T*)x, ids, (const T*)w_up,
-                     (T*)hidden, top, d, ff));
+    if (gated)
+      B200_CUDA(launch(moe_gemv_up_kernel<T, true>, dim3((unsigned)((ff + 7) / 8), (unsigned)(tokens * top)), dim3(256), 0, st, (const T*)x, ids,
+                       (const T*)w_up, (T*)hidden, top, d, ff));
+    else
+      B200_CUDA(launch(moe_gemv_up_kernel<T, false>, dim3((unsigned)((ff + 7) / 8), (unsigned)(tokens * top)), dim3(256), 0, st, (const T*)x, ids,
+                       (const T*)w_up, (T*)hidden, top, d, ff));
     B200_CUDA(launch(moe_gemv_down_kernel<T>, dim3((unsigned)((d + 7) / 8), (unsigned)tokens), dim3(256), 0, st, (const T*)hidden, ids, weights,
                      (const T*)w_down, (T*)out, top, d, ff));
   });

@@ -151,6 +151,99 @@ __global__ void __launch_bounds__(kRowThreads) residual_norm_add_kernel(const T*
   }
 }
 
+
+// Residual update of a block with norms before AND after each sublayer, fused with the norm that feeds the next sublayer:
+//   y    = y0                                   (one branch)
+//        | (norm(y0) * w0 + norm(y1) * w1) / 2  (two mixers side by side, each RMS-normed over the width with its own weight)
+//   x   += norm(y) * post_w  [+ extra]          (fp32 stream; `extra`: e.g. the embedding re-entering before a repeated pass)
+//   act  = T(norm(x) * pre_w)                   (input of the next sublayer; skipped without pre_w)
+// norm(z) = z / sqrt(mean(z^2) + eps), statistics in fp32.  One CTA per row; the row lives in shared memory between the passes.
+struct SandwichArgs {
+  const void* y0; const void* w0; const void* y1; const void* w1;
+  const void* post_w; const float* extra; const void* pre_w;
+  float* x; void* act;
+  int d;
+  float eps;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) sandwich_residual_kernel(SandwichArgs A) {
+  extern __shared__ float sw_row[];   // [d]
+  __shared__ float s_part[kRowThreads / 32];
+  griddep_launch();
+  griddep_wait();
+  const int64_t row = blockIdx.x;
+  const int d = A.d;
+  const T* y0 = reinterpret_cast<const T*>(A.y0) + row * d;
+  const T* y1 = A.y1 ? reinterpret_cast<const T*>(A.y1) + row * d : nullptr;
+  float* xr = A.x + row * d;
+  float s0 = 0.f, s1 = 0.f;
+  for (int i = threadIdx.x; i < d; i += kRowThreads) {
+    const float a = load_as_float(y0, i);
+    s0 = fmaf(a, a, s0);
+    if (y1) { const float b = load_as_float(y1, i); s1 = fmaf(b, b, s1); }
+  }
+  float ss = 0.f;
+  if (y1) {
+    const float r0 = 1.0f / sqrtf(cta_sum(s0, s_part) / (float)d + A.eps);
+    const float r1 = 1.0f / sqrtf(cta_sum(s1, s_part) / (float)d + A.eps);
+    const T* w0 = reinterpret_cast<const T*>(A.w0);
+    const T* w1 = reinterpret_cast<const T*>(A.w1);
+    for (int i = threadIdx.x; i < d; i += kRowThreads) {
+      const float v = 0.5f * (load_as_float(y0, i) * r0 * load_as_float(w0, i) + load_as_float(y1, i) * r1 * load_as_float(w1, i));
+      sw_row[i] = v;
+      ss = fmaf(v, v, ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += kRowThreads) sw_row[i] = load_as_float(y0, i);
+    ss = s0;
+  }
+  float rp = 1.0f;
+  const T* pw = reinterpret_cast<const T*>(A.post_w);
+  if (pw) rp = 1.0f / sqrtf(cta_sum(ss, s_part) / (float)d + A.eps);
+  float sx = 0.f;
+  for (int i = threadIdx.x; i < d; i += kRowThreads) {   // each thread touches only the elements it wrote: no barrier needed
+    float v = xr[i] + (pw ? sw_row[i] * rp * load_as_float(pw, i) : sw_row[i]);
+    if (A.extra) v += A.extra[row * d + i];
+    xr[i] = v;
+    sw_row[i] = v;
+    sx = fmaf(v, v, sx);
+  }
+  if (!A.pre_w) return;
+  const T* nw = reinterpret_cast<const T*>(A.pre_w);
+  T* ar = reinterpret_cast<T*>(A.act) + row * d;
+  const float rn = 1.0f / sqrtf(cta_sum(sx, s_part) / (float)d + A.eps);
+  for (int i = threadIdx.x; i < d; i += kRowThreads) store_from_float(ar, i, sw_row[i] * rn * load_as_float(nw, i));
+}
+
+// elementwise activations: kind 0 exact gelu (erf), 1 tanh gelu, 2 silu, 3 relu^2
+__device__ __forceinline__ float activate(float z, int kind) {
+  if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  if (kind == 2) return z / (1.0f + expf(-z));
+  const float r = fmaxf(z, 0.f);
+  return r * r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) activation_kernel(T* __restrict__ x, int64_t n, int kind) {
+  griddep_launch();
+  griddep_wait();
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) store_from_float(x, i, activate(load_as_float(x, i), kind));
+}
+
+// out[r, c] = act(in[r, c]) * in[r, ff + c]: the gated feed-forward's middle step over a fused [gate | up] product
+template <typename T>
+__global__ void __launch_bounds__(256) glu_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows, int ff, int kind) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t n = rows * ff;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const int64_t r = i / ff, c = i - r * ff;
+    store_from_float(out, i, activate(load_as_float(in, r * 2 * ff + c), kind) * load_as_float(in, r * 2 * ff + ff + c));
+  }
+}
+
 template <typename T, typename I>
 __global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(const T* __restrict__ src, const I* __restrict__ rows,
                                                                    T* __restrict__ dst, int d) {
@@ -265,6 +358,42 @@ int b200_scale_f32(const void* in, float scale, float* out, int64_t n, int dtype
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(scale_f32_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)in, scale, out, n)));
+  return B200_OK;
+}
+
+int b200_sandwich_residual(const b200_sandwich_args* a, b200_stream_t stream) {
+  B200_CHECK_ARG(a && a->y0 && a->x, "b200_sandwich_residual: null pointer");
+  B200_CHECK_ARG(!a->y1 || (a->w0 && a->w1), "b200_sandwich_residual: two branches need their two norm weights");
+  B200_CHECK_ARG(!a->pre_w || a->act, "b200_sandwich_residual: the next sublayer's norm needs somewhere to go");
+  B200_CHECK_ARG(a->rows > 0 && a->rows <= 0x7fffffff && a->d > 0 && (size_t)a->d * sizeof(float) <= 160 * 1024, "b200_sandwich_residual: bad shape");
+  const SandwichArgs A{a->y0, a->w0, a->y1, a->w1, a->post_w, a->extra, a->pre_w, a->x, a->act, a->d, a->eps};
+  const size_t smem = (size_t)a->d * sizeof(float);
+  B200_FLOAT_TYPES(a->dtype, T, {
+    static PerDeviceOnce once;
+    if (smem > 48 * 1024 && once.need()) {
+      B200_CUDA(cudaFuncSetAttribute(sandwich_residual_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      once.done();
+    }
+    B200_CUDA(launch(sandwich_residual_kernel<T>, dim3((unsigned)a->rows), dim3(kRowThreads), smem, (cudaStream_t)stream, A));
+  });
+  return B200_OK;
+}
+
+int b200_activation(void* x, int64_t n, int kind, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(x && n > 0 && kind >= 0 && kind <= 3, "b200_activation: bad argument");
+  int64_t blocks = (n + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(activation_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (T*)x, n, kind)));
+  return B200_OK;
+}
+
+int b200_glu(const void* in, void* out, int64_t rows, int ff, int kind, int dtype, b200_stream_t stream) {
+  B200_CHECK_ARG(in && out && rows > 0 && ff > 0 && kind >= 0 && kind <= 3, "b200_glu: bad argument");
+  int64_t blocks = (rows * ff + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(glu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)in, (T*)out, rows, ff, kind)));
   return B200_OK;
 }
 

@@ -340,7 +340,7 @@ def _main_registered(prompt: str, num_samples: int, max_new_tokens: int, top_k: 
     (``model.safetensors`` weights).  Without tokenizer files the prompt is a list of token ids ("3 17 250" or "3,17,250") and
     ids are printed."""
     from lit_gpt_b200.config import load_config, model_class
-    from lit_gpt_b200.pomipel import Pomipel, load_pomipel
+    from lit_gpt_b200.checkpoint import load_registered
 
     if quantize is not None:
         raise ValueError("Quantization is not supported for this architecture.")
@@ -348,7 +348,7 @@ def _main_registered(prompt: str, num_samples: int, max_new_tokens: int, top_k: 
     if dtype is None:
         raise ValueError(f"--precision {precision!r}: this architecture runs in bf16-true or 32-true")
     config = load_config(checkpoint_dir)
-    if model_class(config) is not Pomipel:
+    if not hasattr(model_class(config), "step"):
         raise ValueError(f"no generate entry point for {type(config).__name__}")
     fabric = Fabric(devices=1, precision=precision)
     has_tokenizer = (checkpoint_dir / "tokenizer.json").is_file() or (checkpoint_dir / "tokenizer.model").is_file()
@@ -363,7 +363,7 @@ def _main_registered(prompt: str, num_samples: int, max_new_tokens: int, top_k: 
         tokenizer, eos_id = None, None
     max_returned_tokens = encoded.size(0) + max_new_tokens
     t0 = time.perf_counter()
-    model = load_pomipel(checkpoint_dir, dtype=dtype, device=fabric.device)
+    model = load_registered(checkpoint_dir, dtype=dtype, device=fabric.device)
     model.max_seq_length = min(max_returned_tokens, config.block_size)
     model.set_kv_cache(batch_size=1)
     fabric.print(f"Time to load the model weights: {time.perf_counter() - t0:.02f} seconds.", file=sys.stderr)

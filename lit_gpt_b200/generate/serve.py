@@ -3,8 +3,8 @@ the replay of a recorded trace of steps.
 
 ``Session`` owns what a set of live requests needs: the model's caches (grown when more requests are live than there are
 slots), one cache slot and the number of cached tokens per request.  ``Session.step`` is the one step function: every entry
-brings the next tokens of a request, all entries run as one ragged batch (``Pomipel.step``), finished requests give their
-slots back.  ``generate_batch`` schedules prompts through it (prefill together, then one token per live request and step,
+brings the next tokens of a request, all entries run as one ragged batch (the model's ``step``), finished requests give their
+slots back; the model is any that serves sequences from slots (``ragged.SlotServed`` with a ``step``: Pomipel, Lefalix).  ``generate_batch`` schedules prompts through it (prefill together, then one token per live request and step,
 shorter requests leaving the batch early); ``Replayer`` feeds it recorded steps instead of sampled tokens.
 """
 from __future__ import annotations
@@ -26,15 +26,14 @@ class Session:
         self.live: Dict[Any, List[int]] = {}    # request id -> [slot, cached tokens]
 
     def _grow(self) -> None:
-        """Twice the slots, the live requests' latents carried over (slot numbers stay)."""
+        """Twice the slots, the live requests' caches and states carried over (slot numbers stay)."""
         model = self.model
-        old = [(b.mixer.cache.latents if b.mixer.cache is not None else None) for b in model.blocks]
+        old = model.state_tensors()
         taken = {slot for slot, _ in self.live.values()}
         capacity = model.slots.capacity
         model.set_kv_cache(batch_size=2 * capacity)
-        for block, prev in zip(model.blocks, old):
-            if prev is not None:
-                block.mixer.cache.latents[:capacity].copy_(prev)
+        for new, prev in zip(model.state_tensors(), old):
+            new[:capacity].copy_(prev)
         model.slots._free = [s for s in range(2 * capacity) if s not in taken]
 
     def step(self, entries: Sequence[Tuple[Any, Sequence[int], Optional[Sequence[int]]]], end: Iterable[Any] = ()) -> Optional[torch.Tensor]:
@@ -120,10 +119,10 @@ class Replayer:
         cls = model_class(config)
         if not hasattr(cls, "step"):
             raise SystemExit(f"{cls.__name__} has no ragged step function: traces replay on models served through Session only")
-        from lit_gpt_b200.pomipel import load_pomipel
+        from lit_gpt_b200.checkpoint import load_registered
 
-        self.model = load_pomipel(model_dir, dtype=dtype, device=device)
-        slots = max(1, -(-max_tokens // self.model.max_seq_length)) if max_tokens else 2
+        self.model = load_registered(model_dir, dtype=dtype, device=device)
+        slots = max(1, min(64, -(-max_tokens // self.model.max_seq_length))) if max_tokens else 2
         self.session = Session(self.model, slots=slots)
 
     def step(self, entries: Sequence[Dict[str, Any]], end: Iterable[Any] = ()) -> Optional[torch.Tensor]:

@@ -7,12 +7,13 @@ from __future__ import annotations
 
 import ctypes
 import functools
-from typing import Dict, Optional, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 import torch._dynamo
 
 from . import _cabi as C
+from ._cabi import ACT_GELU, ACT_GELU_TANH, ACT_RELU2, ACT_SILU  # noqa: F401  (activation kinds of activation_ / glu)
 
 QTYPES = {"nf4": C.Q_NF4, "fp4": C.Q_FP4, "int4": C.Q_INT4}
 _workspaces: Dict[Tuple[str, int], torch.Tensor] = {}
@@ -586,15 +587,16 @@ def _code(t: torch.Tensor) -> int:
     return C.DTYPE_CODE[t.dtype]
 
 
-def embed_pos(tokens: torch.Tensor, pos: torch.Tensor, embed: torch.Tensor, pos_table: Optional[torch.Tensor], scale: float):
-    """tokens, pos int32 (n,) -> (x fp32 (n, d), act T (n, d)) with x = embed[tokens] * scale + pos_table[pos]."""
+def embed_pos(tokens: torch.Tensor, pos: Optional[torch.Tensor], embed: torch.Tensor, pos_table: Optional[torch.Tensor], scale: float):
+    """tokens, pos int32 (n,) -> (x fp32 (n, d), act T (n, d)) with x = embed[tokens] * scale + pos_table[pos]; without a
+    position table (pos None) x = embed[tokens] * scale."""
     C.require_cuda(tokens, pos, embed, pos_table)
-    if tokens.dtype != torch.int32 or pos.dtype != torch.int32:
+    if tokens.dtype != torch.int32 or (pos is not None and pos.dtype != torch.int32) or (pos is None and pos_table is not None):
         raise C.B200Error("embed_pos: tokens and pos must be int32")
     n, d = tokens.numel(), embed.shape[1]
     x = torch.empty((n, d), dtype=torch.float32, device=embed.device)
     act = torch.empty((n, d), dtype=embed.dtype, device=embed.device)
-    C.check(C.load_core().b200_embed_pos(tokens.data_ptr(), pos.data_ptr(), embed.data_ptr(), C.ptr(pos_table), float(scale), x.data_ptr(),
+    C.check(C.load_core().b200_embed_pos(tokens.data_ptr(), C.ptr(pos), embed.data_ptr(), C.ptr(pos_table), float(scale), x.data_ptr(),
                                          act.data_ptr(), n, d, embed.shape[0], 0 if pos_table is None else pos_table.shape[0], _code(embed),
                                          C.stream_ptr(embed.device)), "embed_pos")
     return x, act
@@ -711,37 +713,44 @@ def latent_decode_tune(force_any_size_kernel: bool = False) -> bool:
     return bool(C.load_core().b200_latent_decode_tune(int(force_any_size_kernel)))
 
 
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_group: int, keep: int):
-    """-> (ids int32 (n, top), weights fp32 (n, top)); see b200_moe_route."""
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_group: int, keep: int,
+              softmax: bool = False, group_max: bool = False):
+    """-> (ids int32 (n, top), weights fp32 (n, top)); see b200_moe_route.  softmax: scores are a softmax over all experts
+    instead of sigmoids; group_max: a group ranks by its largest score instead of the sum of its two largest."""
     C.require_cuda(x, w_router, correction)
     n, d = x.shape
     E = w_router.shape[0]
     ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=x.device)
     C.check(C.load_core().b200_moe_route(x.data_ptr(), w_router.data_ptr(), C.ptr(correction), ids.data_ptr(), wts.data_ptr(), n, d, E, top, n_group,
-                                         keep, _code(x), C.stream_ptr(x.device)), "moe_route")
+                                         keep, (C.ROUTE_SOFTMAX if softmax else 0) | (C.ROUTE_GROUP_MAX if group_max else 0), _code(x),
+                                         C.stream_ptr(x.device)), "moe_route")
     return ids, wts
 
 
 MOE_GEMV_MAX_PAIRS = 64   # up to this many (token, choice) pairs the experts run as weight-streaming GEMVs
 
 
-def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum_k wts[t, k] * W_down[ids[t, k]] relu(W_up[ids[t, k]] x[t])^2 with stacked weights (E, ff, d) / (E, d, ff)."""
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, gated: bool = False) -> torch.Tensor:
+    """out[t] = sum_k wts[t, k] * W_down[ids[t, k]] relu(W_up[ids[t, k]] x[t])^2 with stacked weights (E, ff, d) / (E, d, ff);
+    gated: W_up is (E, 2 ff, d), gate rows first, and the hidden vector is silu(gate) * up."""
     C.require_cuda(x, ids, wts, w_up, w_down)
     n, d = x.shape
-    E, ff, top = w_up.shape[0], w_up.shape[1], ids.shape[1]
+    E, ff, top = w_up.shape[0], w_down.shape[2], ids.shape[1]
     lib, st, code = C.load_core(), C.stream_ptr(x.device), _code(x)
     out = torch.empty((n, d), dtype=x.dtype, device=x.device)
     if n * top <= MOE_GEMV_MAX_PAIRS:
         hidden = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
         C.check(lib.b200_moe_gemv(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), hidden.data_ptr(), out.data_ptr(),
-                                  n, top, d, ff, code, st), "moe_gemv")
+                                  n, top, d, ff, int(gated), code, st), "moe_gemv")
         return out
     plan = moe_plan(ids, E)
-    hidden = torch.empty((n * top, ff), dtype=x.dtype, device=x.device)
-    C.check(lib.b200_moe_gemm(x.data_ptr(), x.stride(0), plan.slot_token.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), ff, plan.expert_off.data_ptr(),
-                              plan.tile_off.data_ptr(), n * top, E, ff, d, 1, code, st), "moe_gemm(up)")
+    up_rows = 2 * ff if gated else ff
+    hidden = torch.empty((n * top, up_rows), dtype=x.dtype, device=x.device)
+    C.check(lib.b200_moe_gemm(x.data_ptr(), x.stride(0), plan.slot_token.data_ptr(), w_up.data_ptr(), hidden.data_ptr(), up_rows,
+                              plan.expert_off.data_ptr(), plan.tile_off.data_ptr(), n * top, E, up_rows, d, 0 if gated else 1, code, st), "moe_gemm(up)")
+    if gated:
+        hidden = glu(hidden, C.ACT_SILU)
     y = torch.empty((n * top, d), dtype=x.dtype, device=x.device)
     C.check(lib.b200_moe_gemm(hidden.data_ptr(), ff, None, w_down.data_ptr(), y.data_ptr(), d, plan.expert_off.data_ptr(), plan.tile_off.data_ptr(),
                               n * top, E, d, ff, 0, code, st), "moe_gemm(down)")
@@ -775,3 +784,148 @@ def moe_combine(y: torch.Tensor, plan: MoEPlan, wts: torch.Tensor) -> torch.Tens
     C.check(C.load_core().b200_moe_combine(y.data_ptr(), plan.slot_of.data_ptr(), wts.data_ptr(), out.data_ptr(), plan.tokens, plan.top, d, _code(y),
                                            C.stream_ptr(y.device)), "moe_combine")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# sequence-state mechanisms: sandwich-normed residual, short convolutions, gated delta rule, windowed attention over a ring
+# (csrc/resid.cu, shortconv.cu, delta.cu, window_attn.cu).  A step's rows are described by ``seqs`` int32 (S, 4) = first row,
+# rows, first position, state slot, and ``row_seq`` int32 (n,).
+# ---------------------------------------------------------------------------------------------------------
+def sandwich_residual(x: torch.Tensor, y0: torch.Tensor, post_w: Optional[torch.Tensor], eps: float, *, w0: Optional[torch.Tensor] = None,
+                      y1: Optional[torch.Tensor] = None, w1: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
+                      pre_w: Optional[torch.Tensor] = None, act: Optional[torch.Tensor] = None) -> None:
+    """x (fp32, in place) += norm(y) * post_w [+ extra]; act = T(norm(x) * pre_w).  y = y0, or with y1 the mean of the two branches
+    each normed with its weight (w0, w1)."""
+    C.require_cuda(x, y0, y1, post_w, extra, pre_w, act)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not y0.is_contiguous() or (y1 is not None and not y1.is_contiguous()):
+        raise C.B200Error("sandwich_residual: x must be contiguous fp32, the branches contiguous")
+    if extra is not None and (extra.dtype != torch.float32 or not extra.is_contiguous()):
+        raise C.B200Error("sandwich_residual: extra must be contiguous fp32")
+    d = x.shape[-1]
+    args = C.SandwichArgs(y0=y0.data_ptr(), w0=C.ptr(w0), y1=C.ptr(y1), w1=C.ptr(w1), post_w=C.ptr(post_w), extra=C.ptr(extra), pre_w=C.ptr(pre_w),
+                          x=x.data_ptr(), act=C.ptr(act), rows=x.numel() // d, d=d, eps=float(eps), dtype=_code(y0))
+    C.check(C.load_core().b200_sandwich_residual(ctypes.byref(args), C.stream_ptr(x.device)), "sandwich_residual")
+
+
+def activation_(x: torch.Tensor, kind: int) -> torch.Tensor:
+    """In place: C.ACT_GELU (erf), C.ACT_GELU_TANH, C.ACT_SILU, C.ACT_RELU2."""
+    C.require_cuda(x)
+    if not x.is_contiguous():
+        raise C.B200Error("activation_: contiguous tensor")
+    C.check(C.load_core().b200_activation(x.data_ptr(), x.numel(), kind, _code(x), C.stream_ptr(x.device)), "activation")
+    return x
+
+
+def glu(x: torch.Tensor, kind: int) -> torch.Tensor:
+    """x (rows, 2 ff) = [gate | up] -> act(gate) * up (rows, ff)."""
+    C.require_cuda(x)
+    if not x.is_contiguous() or x.shape[-1] % 2:
+        raise C.B200Error("glu: contiguous rows of even length")
+    ff = x.shape[-1] // 2
+    out = torch.empty(x.shape[:-1] + (ff,), dtype=x.dtype, device=x.device)
+    C.check(C.load_core().b200_glu(x.data_ptr(), out.data_ptr(), x.numel() // (2 * ff), ff, kind, _code(x), C.stream_ptr(x.device)), "glu")
+    return out
+
+
+def conv_group(w: torch.Tensor, out: torch.Tensor, col0: int, heads: int, dim: int, *, act: int = 0, post: int = 0, rot_dims: int = 0,
+               inv_freq: Optional[torch.Tensor] = None, rot_mscale: float = 1.0, post_scale: float = 1.0, eps: float = 0.0) -> "C.ConvGroup":
+    """One group of heads for ``short_conv``: act 0 none / 1 silu; post 0 none / 1 rotate + RMS norm / 2 unit vector."""
+    if not w.is_contiguous() or out.stride(-1) != 1 or out.dtype not in (w.dtype, torch.float32):
+        raise C.B200Error("conv_group: contiguous weights, output rows in the model dtype or fp32")
+    if inv_freq is not None and (inv_freq.dtype != torch.float64 or inv_freq.numel() < rot_dims // 2 or not inv_freq.is_cuda):
+        raise C.B200Error("conv_group: inv_freq must be a CUDA float64 tensor of rot_dims / 2 entries")
+    return C.ConvGroup(w=w.data_ptr(), out=out.data_ptr(), ld_out=out.stride(-2), inv_freq=C.ptr(inv_freq), col0=col0, heads=heads, dim=dim,
+                       act=act, post=post, rot_dims=rot_dims, out_f32=int(out.dtype == torch.float32 and w.dtype != torch.float32),
+                       rot_mscale=float(rot_mscale), post_scale=float(post_scale), eps=float(eps))
+
+
+def short_conv(inp: torch.Tensor, groups: Sequence["C.ConvGroup"], taps: int, tail: Optional[torch.Tensor], seqs: torch.Tensor,
+               row_seq: torch.Tensor) -> None:
+    """Causal convolution over `taps` positions on the first tail.shape[-1] columns of inp (rows, cols), per group of heads with
+    its activation and per-head step; tail (slots, taps - 1, conv_cols) holds what earlier steps left, and is updated."""
+    C.require_cuda(inp, tail, seqs, row_seq)
+    if inp.stride(-1) != 1 or seqs.dtype != torch.int32 or row_seq.dtype != torch.int32 or not seqs.is_contiguous():
+        raise C.B200Error("short_conv: unit inner stride, int32 seqs and row_seq")
+    if tail is not None and (tail.dtype != inp.dtype or not tail.is_contiguous()):
+        raise C.B200Error("short_conv: the tail must be contiguous in the model dtype")
+    lib, st = C.load_core(), C.stream_ptr(inp.device)
+    arr = (C.ConvGroup * len(groups))(*groups)
+    cols = sum(g.heads * g.dim for g in groups) if tail is None else tail.shape[-1]
+    stride = 0 if tail is None else tail.stride(0)
+    C.check(lib.b200_short_conv(inp.data_ptr(), inp.stride(0), arr, len(groups), taps, C.ptr(tail), stride, cols, seqs.data_ptr(), row_seq.data_ptr(),
+                                inp.shape[0], _code(inp), st), "short_conv")
+    if tail is not None and taps > 1:
+        C.check(lib.b200_conv_tail_update(inp.data_ptr(), inp.stride(0), tail.data_ptr(), stride, cols, taps, seqs.data_ptr(), seqs.shape[0],
+                                          _code(inp), st), "conv_tail_update")
+
+
+def delta_rule_state_floats(dk: int, dv: int) -> int:
+    """fp32 numbers one head's state takes in the kernel's own order."""
+    return int(C.load_core().b200_delta_rule_state_floats(dk, dv))
+
+
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_in: torch.Tensor, decay_in: torch.Tensor, a_log: torch.Tensor,
+               dt_bias: torch.Tensor, state: torch.Tensor, seqs: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int,
+               channel_decay: bool) -> torch.Tensor:
+    """Gated delta rule over the step's rows; state (slots, floats) fp32 is read (unless the sequence starts at 0) and written.
+    q, k (n, kv_heads * dk), v (n, heads * dv) fp32; beta_in (n, heads), decay_in (n, heads [* dk]) raw projections.  -> fp32 (n, heads * dv)"""
+    C.require_cuda(q, k, v, beta_in, decay_in, a_log, dt_bias, state, seqs)
+    if not (q.dtype == k.dtype == v.dtype == state.dtype == torch.float32) or seqs.dtype != torch.int32 or not seqs.is_contiguous():
+        raise C.B200Error("delta_rule: q, k, v and the state are fp32, seqs int32")
+    if beta_in.dtype != decay_in.dtype or a_log.dtype != beta_in.dtype or dt_bias.dtype != beta_in.dtype:
+        raise C.B200Error("delta_rule: projections and parameters in one dtype")
+    for t in (q, k, v, beta_in, decay_in):
+        if t.stride(-1) != 1:
+            raise C.B200Error("delta_rule: unit inner strides")
+    if state.stride(0) < heads * delta_rule_state_floats(dk, dv) or not state.is_contiguous():
+        raise C.B200Error("delta_rule: the state slots are too small")
+    out = torch.empty((q.shape[0], heads * dv), dtype=torch.float32, device=q.device)
+    args = C.DeltaRuleArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
+                           beta_in=beta_in.data_ptr(), ld_beta=beta_in.stride(0), decay_in=decay_in.data_ptr(), ld_decay=decay_in.stride(0),
+                           a_log=a_log.data_ptr(), dt_bias=dt_bias.data_ptr(), state=state.data_ptr(), state_slot_stride=state.stride(0),
+                           out=out.data_ptr(), ldo=out.stride(0), seqs=seqs.data_ptr(), n_seqs=seqs.shape[0], heads=heads, kv_heads=kv_heads,
+                           dk=dk, dv=dv, channel_decay=int(channel_decay), dtype=_code(beta_in))
+    C.check(C.load_core().b200_delta_rule(ctypes.byref(args), C.stream_ptr(q.device)), "delta_rule")
+    return out
+
+
+GATE_SILU, GATE_SIGMOID = 1, 2
+
+
+def gated_rms_heads(o: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, heads: int, dv: int, gate: int, eps: float) -> torch.Tensor:
+    """o fp32 (n, heads * dv), z (n, heads * dv) raw gate projection -> T (n, heads * dv): per-head RMS norm * weight * gate(z)."""
+    C.require_cuda(o, z, weight)
+    if o.dtype != torch.float32 or o.stride(-1) != 1 or z.stride(-1) != 1 or z.dtype != weight.dtype:
+        raise C.B200Error("gated_rms_heads: o fp32, gate and weight in the model dtype")
+    out = torch.empty((o.shape[0], heads * dv), dtype=z.dtype, device=o.device)
+    C.check(C.load_core().b200_gated_rms_heads(o.data_ptr(), o.stride(0), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0),
+                                               o.shape[0], heads, dv, gate, float(eps), _code(z), C.stream_ptr(o.device)), "gated_rms_heads")
+    return out
+
+
+def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch.Tensor, v_ring: torch.Tensor, sink: Optional[torch.Tensor],
+                seqs: torch.Tensor, row_seq: torch.Tensor, max_q_len: int, n_head: int, n_kv_head: int, dk: int, dv: int, window: int,
+                scale: float) -> torch.Tensor:
+    """Sliding-window attention with a sink over this step's k / v rows and the rings (slots, ring, G * dk | dv) of earlier
+    positions; afterwards the step's rows enter the rings.  -> (n, n_head * dv)"""
+    C.require_cuda(q, k, v, k_ring, v_ring, sink, seqs, row_seq)
+    if not (q.dtype == k.dtype == v.dtype == k_ring.dtype == v_ring.dtype) or not (k_ring.is_contiguous() and v_ring.is_contiguous()):
+        raise C.B200Error("window_attn: one dtype, contiguous rings")
+    if q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1 or seqs.dtype != torch.int32 or not seqs.is_contiguous():
+        raise C.B200Error("window_attn: unit inner strides, int32 seqs")
+    ring = k_ring.shape[1]
+    out = torch.empty((q.shape[0], n_head * dv), dtype=q.dtype, device=q.device)
+    lib, st = C.load_core(), C.stream_ptr(q.device)
+    args = C.WindowAttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
+                            ldo=out.stride(0), k_ring=k_ring.data_ptr(), v_ring=v_ring.data_ptr(), sink=C.ptr(sink), seqs=seqs.data_ptr(),
+                            n_seqs=seqs.shape[0], max_q_len=max_q_len, ring=ring, n_head=n_head, n_kv_head=n_kv_head, dk=dk, dv=dv, window=window,
+                            scale=float(scale), dtype=_code(q))
+    C.check(lib.b200_window_attn(ctypes.byref(args), st), "window_attn")
+    C.check(lib.b200_ring_store(k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_ring.data_ptr(), v_ring.data_ptr(), ring, n_kv_head * dk,
+                                n_kv_head * dv, seqs.data_ptr(), row_seq.data_ptr(), q.shape[0], _code(q), st), "ring_store")
+    return out
+
+
+def window_attn_tune(force_tiled_kernel: bool = False) -> bool:
+    """Test knob: keep single-row steps on the tiled kernel; returns the previous setting."""
+    return bool(C.load_core().b200_window_attn_tune(int(force_tiled_kernel)))

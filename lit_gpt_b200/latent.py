@@ -21,6 +21,7 @@ import torch.nn.functional as F
 
 from . import kernels as K
 from .config import LatentMixerSpec
+from .ragged import RaggedBatch  # noqa: F401  (re-exported)
 
 DECODE_KEYS_PER_SPLIT = 64
 DECODE_MAX_SPLITS = 64
@@ -33,21 +34,6 @@ def decode_splits(context: int, rows: int = 1) -> int:
     """CTAs that share one (sequence, head tile) of a decode step over a context of at most `context` positions: 64-key ranges,
     but no more splits than it takes `rows` (sequences x head tiles) to fill the GPU twice."""
     return max(1, min(DECODE_MAX_SPLITS, -(-context // DECODE_KEYS_PER_SPLIT), max(1, DECODE_TARGET_CTAS // max(rows, 1))))
-
-
-@dataclass
-class RaggedBatch:
-    """Device-side description of one step.  n rows (tokens) of S sequences."""
-
-    row_pos: torch.Tensor            # int32 (n,)   position of each row in its sequence
-    row_slot: torch.Tensor           # int32 (n,)   cache slot of each row
-    cache_rows: torch.Tensor         # int64 (n,)   slot * max_seq + position: where the row's latent is stored
-    decode: bool                     # every sequence brings exactly one row
-    context_hint: int                # upper bound of any row's position + 1 (sizes the decode split)
-    seqs: Optional[torch.Tensor] = None        # int32 (S, 4): first row, rows, first position, first row of its context in ctx_rows
-    ctx_rows: Optional[torch.Tensor] = None    # int64 (m,)   cache rows of every sequence's whole context, sequence after sequence
-    max_q_len: int = 1
-    identity_ctx: bool = False       # every sequence starts at position 0: the context rows ARE the step's rows, in order
 
 
 class LatentCache(nn.Module):

@@ -25,31 +25,9 @@ import torch.nn.functional as F
 
 from . import kernels as K
 from .config import PomipelConfig
-from .latent import LatentAttention, RaggedBatch
+from .latent import LatentAttention
 from .moe import SparseExperts
-
-
-class SlotAllocator:
-    """Hands out cache slots (rows of the latent caches) to live sequences; a released slot is reused, lowest first."""
-
-    def __init__(self, slots: int) -> None:
-        self.capacity = slots
-        self._free = list(range(slots))
-
-    def acquire(self) -> int:
-        if not self._free:
-            raise RuntimeError(f"all {self.capacity} cache slots are in use")
-        self._free.sort()
-        return self._free.pop(0)
-
-    def release(self, slot: int) -> None:
-        if not 0 <= slot < self.capacity or slot in self._free:
-            raise ValueError(f"slot {slot} is not in use")
-        self._free.append(slot)
-
-    @property
-    def in_use(self) -> int:
-        return self.capacity - len(self._free)
+from .ragged import RaggedBatch, SlotAllocator, SlotServed
 
 
 class PomipelBlock(nn.Module):
@@ -69,8 +47,7 @@ class PomipelBlock(nn.Module):
             K.residual_norm_add(self.mlp(act), self.norm_2, self.eps, x, act)
 
 
-class Pomipel(nn.Module):
-    supports_prefill_graph = False   # a prompt's context length is read on the host
+class Pomipel(SlotServed, nn.Module):
 
     def __init__(self, config: PomipelConfig) -> None:
         super().__init__()
@@ -87,27 +64,8 @@ class Pomipel(nn.Module):
         self.head = nn.Parameter(torch.empty(config.vocab_size, d), requires_grad=False)
         self._max_seq_length = config.block_size
         self.slots: Optional[SlotAllocator] = None
-        self.tp_world_size = 1
 
-    # ---- the surface generate() uses ------------------------------------------------------------------------------
-    @property
-    def max_seq_length(self) -> int:
-        return self._max_seq_length
-
-    @max_seq_length.setter
-    def max_seq_length(self, value: int) -> None:
-        if value > self.config.block_size:
-            raise ValueError(f"Cannot attend to {value}, block size is only {self.config.block_size}")
-        self._max_seq_length = value
-
-    @property
-    def dtype(self) -> torch.dtype:
-        return self.embed.dtype
-
-    @property
-    def device(self) -> torch.device:
-        return self.embed.device
-
+    # ---- the surface generate() uses (with ``SlotServed``) --------------------------------------------------------
     def set_kv_cache(self, batch_size: int, rope_cache_length: Optional[int] = None, device: Optional[torch.device] = None,
                      dtype: Optional[torch.dtype] = None) -> None:
         """`batch_size` cache slots of `max_seq_length` positions for every layer that projects its own latents."""
@@ -116,15 +74,13 @@ class Pomipel(nn.Module):
         for block in self.blocks:
             block.mixer.cache = block.mixer.build_cache(batch_size, self.max_seq_length, device, dtype)
         self.slots = SlotAllocator(batch_size)
-        self.__dict__.pop("_decode_graphs", None)   # captured graphs pin the cache buffers
-        self.__dict__.pop("_const", None)
+        self._drop_graphs()
 
     def clear_kv_cache(self) -> None:
         for block in self.blocks:
             block.mixer.cache = None
         self.slots = None
-        self.__dict__.pop("_decode_graphs", None)
-        self.__dict__.pop("_const", None)
+        self._drop_graphs()
 
     def reset_caches(self) -> None:
         for block in self.blocks:
@@ -132,22 +88,11 @@ class Pomipel(nn.Module):
                 block.mixer.cache.reset_parameters()
 
     def _apply(self, fn, recurse: bool = True):
-        self.__dict__.pop("_decode_graphs", None)
-        self.__dict__.pop("_const", None)
+        self._drop_graphs()
         return super()._apply(fn, recurse)
 
-    def fused_decode_ready(self, idx: Optional[torch.Tensor] = None) -> bool:
-        """True when a decode step is made of capturable launches only (CUDA, caches set)."""
-        if idx is not None and not idx.is_cuda:
-            return False
-        return self.embed.is_cuda and self.slots is not None and self.dtype in (torch.bfloat16, torch.float32)
-
-    def spans_devices(self) -> bool:
-        return False
-
-    def graph_key(self) -> Tuple:
-        caches = tuple(b.mixer.cache.latents.data_ptr() for b in self.blocks if b.mixer.cache is not None)
-        return (self.max_seq_length, caches, self.embed.data_ptr(), self.head.data_ptr())
+    def state_tensors(self) -> List[torch.Tensor]:
+        return [b.mixer.cache.latents for b in self.blocks if b.mixer.cache is not None]
 
     # ---- weights ----------------------------------------------------------------------------------------------------
     def reset_parameters(self, seed: int = 1234, std: float = 0.02) -> None:
@@ -206,19 +151,6 @@ class Pomipel(nn.Module):
             raise KeyError(f"unexpected tensors in the checkpoint: {extra[:6]}")
 
     # ---- one step ---------------------------------------------------------------------------------------------------
-    @contextlib.contextmanager
-    def _true_fp32(self) -> Iterator[None]:
-        """fp32 models multiply in fp32: no TF32 inside the vendor GEMM, whatever the process-wide setting is."""
-        if self.dtype != torch.float32:
-            yield
-            return
-        old = torch.backends.cuda.matmul.allow_tf32
-        torch.backends.cuda.matmul.allow_tf32 = False
-        try:
-            yield
-        finally:
-            torch.backends.cuda.matmul.allow_tf32 = old
-
     def _run(self, tokens: torch.Tensor, batch: RaggedBatch, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """tokens int32 (n,) -> fp32 logits (rows wanted or n, vocab)"""
         c = self.config
@@ -301,19 +233,10 @@ class Pomipel(nn.Module):
 
 
 def load_pomipel(checkpoint_dir: Any, dtype: torch.dtype = torch.bfloat16, device: Any = "cuda") -> Pomipel:
-    """Build the model a checkpoint directory (``config.json`` + ``model.safetensors``) describes, on `device` in `dtype`."""
-    from pathlib import Path
+    """Build the Pomipel model of a checkpoint directory (``config.json`` + ``model.safetensors``) on `device` in `dtype`."""
+    from .checkpoint import load_registered
 
-    from .checkpoint import read_safetensors
-    from .config import load_config
-
-    path = Path(checkpoint_dir)
-    config = load_config(path)
-    if not isinstance(config, PomipelConfig):
-        raise TypeError(f"{str(path)!r} does not hold a Pomipel model")
-    with torch.device("meta"):
-        model = Pomipel(config)
-    model = model.to_empty(device=device).to(dtype)
-    tensors = read_safetensors(path / "model.safetensors")
-    model.load_tensors({k: v for k, v in tensors.items() if v.is_floating_point()})
-    return model.eval()
+    model = load_registered(checkpoint_dir, dtype=dtype, device=device)
+    if not isinstance(model, Pomipel):
+        raise TypeError(f"{str(checkpoint_dir)!r} does not hold a Pomipel model")
+    return model
