@@ -103,25 +103,25 @@ def test_session_bookkeeping_with_a_stand_in_model():
 
     calls = []
 
-    class Mixer:
-        cache = None
-
-    class Block:
-        mixer = Mixer()
-
     class Fake:
         max_seq_length = 50
-        blocks = [Block()]
+        marks = None
 
         def set_kv_cache(self, batch_size):
             self.slots = SlotAllocator(batch_size)
+            self.marks = torch.zeros(batch_size, 2)
+
+        def state_tensors(self):
+            return [self.marks]
 
         def step(self, tokens, seqs, want):
             calls.append((list(tokens), list(seqs), list(want)))
             return torch.zeros(len(want), 4)
 
     s = Session(Fake(), slots=1)
-    out = s.step([("a", [1, 2, 3], [2]), ("b", [4], [])])          # b forces the cache to grow
+    s.model.marks[0] = 5.0
+    out = s.step([("a", [1, 2, 3], [2]), ("b", [4], [])])          # b forces the cache to grow: what slot 0 held moves along
+    assert s.model.marks.tolist() == [[5.0, 5.0], [0.0, 0.0]]
     assert out.shape == (1, 4) and calls[-1] == ([1, 2, 3, 4], [(0, 0, 3), (1, 0, 1)], [2])
     assert s.step([("a", [5], []), ("b", [6], [])], end=["a"]) is None      # nothing wanted: nothing returned, the step still runs
     assert calls[-1][1] == [(0, 3, 1), (1, 1, 1)]
