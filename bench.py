@@ -618,6 +618,168 @@ def run_arch_compare(args) -> None:
                       "gpu_launches": int(K.launch_count() - launches0), "sizes": out}), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --compare lefalix: the Lefalix design beside the closest existing model (Pomipel: the other slot-served design with an fp32
+# residual stream and sparse experts) at equal width, heads, head size, layers and expert sizes; random weights.
+# ---------------------------------------------------------------------------------------------------------
+LEFALIX_SIZES = {
+    # name: width, heads, key-value heads, head size, window, low rank, experts, top, expert ff, dense ff
+    "w1024": (1024, 8, 2, 128, 512, 64, 16, 4, 512, 4096),
+    "w2048": (2048, 16, 4, 128, 1024, 128, 32, 4, 1024, 8192),
+    "w4096": (4096, 32, 8, 128, 1024, 128, 64, 6, 1024, 14336),
+}
+
+
+def run_lefalix_compare(args) -> None:
+    from lit_gpt_b200 import kernels as K
+    from lit_gpt_b200.config import (DeltaMixerSpec, DenseMLPSpec, GatedMoESpec, LatentMixerSpec, LayerSpec, LefalixConfig, LefalixLayerSpec, MoESpec,
+                                     ParallelMixerSpec, PomipelConfig, RotarySpec, WindowMixerSpec)
+    from lit_gpt_b200.latent import decode_splits
+    from lit_gpt_b200.lefalix import Lefalix
+    from lit_gpt_b200.pomipel import Pomipel
+    from lit_gpt_b200.ragged import state_batch
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, peak_source = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    vocab, T = 32000, args.prompt
+    iters = max(3, min(args.steps, 20))
+    launches0 = K.launch_count()
+    bf = torch.bfloat16
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else LEFALIX_SIZES):
+        d, H, G, hs, W, rank, E, top, ff, dff = LEFALIX_SIZES[name]
+        rot = RotarySpec(dims=hs // 2, base=1e6, factor=4.0, original=4096.0, fast=32.0, slow=1.0)
+
+        def par(mlp):
+            return LefalixLayerSpec("parallel", ParallelMixerSpec(WindowMixerSpec(H, G, hs, hs, 4, W, hs ** -0.5, rot), DeltaMixerSpec(H // 2, H // 4, hs, hs, 4)), mlp)
+
+        def chan(mlp):
+            return LefalixLayerSpec("channel_delta", DeltaMixerSpec(H, H // 2, hs, hs, 4, True, rank, rank), mlp)
+
+        layers = [chan(DenseMLPSpec(dff)), par(GatedMoESpec(E, top, ff, 4, 2)), par(DenseMLPSpec(dff)), chan(GatedMoESpec(E, top, ff, 4, 2))]
+        lef = Lefalix(LefalixConfig(vocab_size=vocab, n_embd=d, layers=layers)).to(dev).to(bf).eval()
+        lef.reset_parameters()
+        lef.max_seq_length = T + 64
+        players = [LayerSpec("latent_attention", LatentMixerSpec(H, hs, hs, 4 * hs, 8 * hs, hs ** -0.5, None if i % 2 == 0 else i - 1),
+                             MoESpec(E, top, ff, 4, 2)) for i in range(4)]
+        pom = Pomipel(PomipelConfig(vocab_size=vocab, n_embd=d, block_size=T + 64, embedding_scale=d ** 0.5, logit_scale=1.0, layers=players))
+        pom = pom.to(dev).to(bf).eval()
+        pom.reset_parameters()
+        res = {}
+        with torch.inference_mode():
+            for label, model in (("lefalix", lef), ("pomipel", pom)):
+                for B in (1, 8):
+                    model.set_kv_cache(batch_size=B)
+                    idx = torch.randint(0, vocab, (B, T), device=dev)
+                    pos = torch.arange(T, device=dev)
+                    if B == 1:
+                        ms = _timed(lambda: model(idx, pos), iters, flush)
+                        res[f"{label}_prefill_tok_s"] = round(T / ms * 1e3)
+                    else:
+                        model(idx, pos)
+                    tok, p1 = idx[:, :1].contiguous(), torch.tensor([T], device=dev)
+                    step, graphed = _graphed(lambda: model(tok, p1))
+                    ms = _timed(step, iters, flush)
+                    res[f"{label}_decode_b{B}_tok_s"] = round(B / ms * 1e3)
+                    res[f"{label}_decode_b{B}_graphed"] = graphed
+                    del step
+                model.clear_kv_cache()
+            kern = {}
+            # prefill attention: both designs on the same tensor-core tiles; the window's work is T * W - W^2 / 2 score pairs
+            q = torch.randn(T, H * hs, device=dev, dtype=bf)
+            kv = torch.randn(T, 2 * G * hs, device=dev, dtype=bf)
+            sink = torch.zeros(H, device=dev, dtype=bf)
+            batch, _ = state_batch([(0, 0, T)], dev)
+            kr, vr = torch.zeros(1, W, G * hs, device=dev, dtype=bf), torch.zeros(1, W, G * hs, device=dev, dtype=bf)
+            pairs = sum(min(i + 1, W) for i in range(T))
+            ms = _timed(lambda: K.window_attn(q, kv[:, : G * hs], kv[:, G * hs :], kr, vr, sink, batch.seq_state, batch.row_seq, T, H, G, hs, hs, W,
+                                              hs ** -0.5, from_start=True), iters, flush)
+            kern["prefill_attention_lefalix"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * H * hs * pairs / (ms * 1e-3) / tf, "includes": "ring store"}
+            kvp = torch.randn(T, 2 * H * hs, device=dev, dtype=bf)
+            seqs = torch.tensor([[0, T, 0, 0]], dtype=torch.int32, device=dev)
+            ms = _timed(lambda: K.latent_prefill(q, kvp[:, : H * hs], kvp[:, H * hs :], seqs, T, H, hs, hs, hs ** -0.5), iters, flush)
+            kern["prefill_attention_pomipel"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * H * hs * T * (T + 1) / 2 / (ms * 1e-3) / tf}
+            # decode attention: bytes that must come from HBM
+            B = 8
+            qd, kd = torch.randn(B, H * hs, device=dev, dtype=bf), torch.randn(B, 2 * G * hs, device=dev, dtype=bf)
+            krb, vrb = torch.randn(B, W, G * hs, device=dev, dtype=bf), torch.randn(B, W, G * hs, device=dev, dtype=bf)
+            bd, _ = state_batch([(b, T, 1) for b in range(B)], dev)
+            ms = _timed(lambda: K.window_attn(qd, kd[:, : G * hs], kd[:, G * hs :], krb, vrb, sink, bd.seq_state, bd.row_seq, 1, H, G, hs, hs, W,
+                                              hs ** -0.5), iters, flush)
+            roof = 2.0 * B * G * W * hs * 2 / hbm
+            kern["decode_attention_lefalix"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": 2.0 * B * G * W * hs * 2,
+                                                "includes": "ring store"}
+            r = 4 * hs
+            mx = pom.blocks[0].mixer
+            cache = torch.randn(B, T, r, device=dev, dtype=bf)
+            slot = torch.arange(B, dtype=torch.int32, device=dev)
+            rp = torch.full((B,), T - 1, dtype=torch.int32, device=dev)
+            ms = _timed(lambda: K.latent_decode(qd, mx.w_uk, mx.w_uv, cache, slot, rp, H, hs, hs, hs ** -0.5, decode_splits(T, B * (-(-H // 16)))), iters, flush)
+            roof = max(B * T * r * 2 / hbm, 4.0 * B * H * T * r / tf)
+            kern["decode_attention_pomipel"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": B * T * r * 2}
+            # the recurrence: prompts are bound by the chain of T dependent state updates, single tokens by the state's bytes
+            dm = lef.blocks[0].mixer
+            Hd, Gd = dm.spec.heads, dm.spec.kv_heads
+            floats = Hd * K.delta_rule_state_floats(hs, hs)
+            for label, ch in (("channel", True), ("head", False)):
+                qf, kf, vf = torch.randn(T, Gd * hs, device=dev), torch.randn(T, Gd * hs, device=dev), torch.randn(T, Hd * hs, device=dev)
+                be, de = torch.randn(T, Hd, device=dev, dtype=bf), torch.randn(T, Hd * hs if ch else Hd, device=dev, dtype=bf)
+                al, db = torch.zeros(Hd, device=dev, dtype=bf), torch.zeros(Hd * hs if ch else Hd, device=dev, dtype=bf)
+                st1 = torch.zeros(1, floats, device=dev)
+                ms = _timed(lambda: K.delta_rule(qf, kf, vf, be, de, al, db, st1, batch.seq_state, Hd, Gd, hs, hs, ch), iters, flush)
+                kern[f"delta_rule_prompt_{label}_decay"] = {"ms": ms, "us_per_token": ms * 1e3 / T, "fp32_tflops": 6.0 * T * Hd * hs * hs / (ms * 1e-3) / 1e12}
+                st8 = torch.zeros(B, floats, device=dev)
+                ms = _timed(lambda: K.delta_rule(qf[:B], kf[:B], vf[:B], be[:B], de[:B], al, db, st8, bd.seq_state, Hd, Gd, hs, hs, ch), iters, flush)
+                roof = 2.0 * B * floats * 4 / hbm
+                kern[f"delta_rule_decode_{label}_decay"] = {"ms": ms, "roofline_ms": roof * 1e3, "frac_of_roofline": roof / (ms * 1e-3), "bytes": 2.0 * B * floats * 4}
+            # short convolution with rotation and norm (reads bf16 rows, writes bf16 rows) beside Pomipel's norm of projected rows
+            wm = lef.blocks[1].mixer.left
+            cols = wm.cols
+            qkv, dst = torch.randn(T, cols, device=dev, dtype=bf), torch.empty(T, cols, device=dev, dtype=bf)
+            tail = torch.zeros(1, 3, cols, device=dev, dtype=bf)
+            fr = wm.inv_freq(dev)
+            groups = [K.conv_group(wm.conv[: H * hs], dst[:, : H * hs], 0, H, hs, post=1, rot_dims=hs // 2, inv_freq=fr, rot_mscale=rot.magnitude, eps=1e-5),
+                      K.conv_group(wm.conv[H * hs : (H + G) * hs], dst[:, H * hs : (H + G) * hs], H * hs, G, hs, post=1, rot_dims=hs // 2, inv_freq=fr,
+                                   rot_mscale=rot.magnitude, eps=1e-5),
+                      K.conv_group(wm.conv[(H + G) * hs :], dst[:, (H + G) * hs :], (H + G) * hs, G, hs)]
+            ms = _timed(lambda: K.short_conv(qkv, groups, 4, tail, batch.seq_state, batch.row_seq), iters, flush)
+            kern["short_conv_rotate_norm_lefalix"] = {"ms": ms, "frac_of_measured_hbm": T * cols * 4.0 / (ms * 1e-3) / hbm}
+            down, cq = torch.randn(T, cols, device=dev, dtype=bf), torch.empty(T, cols, device=dev, dtype=bf)
+            wn = torch.ones(cols, device=dev, dtype=bf)
+            ms = _timed(lambda: K.rms_rows(T, 1e-5, K.rms_seg(down, wn, cq, cols, False), in_dtype=bf, out_dtype=bf, device=dev), iters, flush)
+            kern["norm_of_projected_rows_pomipel"] = {"ms": ms, "frac_of_measured_hbm": T * cols * 4.0 / (ms * 1e-3) / hbm}
+            # residual kernels
+            x = torch.randn(T, d, device=dev, dtype=bf)
+            x2 = torch.randn(T, d, device=dev, dtype=bf)
+            xs, act = torch.randn(T, d, device=dev), torch.empty(T, d, device=dev, dtype=bf)
+            blk = lef.blocks[1]
+            ms = _timed(lambda: K.sandwich_residual(xs, x, blk.norm_1b, 1e-5, w0=blk.mixer.left_out, y1=x2, w1=blk.mixer.right_out, pre_w=blk.norm_2, act=act),
+                        iters, flush)
+            kern["residual_two_branches_lefalix"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.sandwich_residual(xs, x, blk.norm_2b, 1e-5, pre_w=blk.norm_1, act=act), iters, flush)
+            kern["residual_one_branch_lefalix"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            ms = _timed(lambda: K.residual_norm_add(x, pom.blocks[0].norm_1, 1e-5, xs, act), iters, flush)
+            kern["residual_norm_pomipel"] = {"ms": ms, "frac_of_measured_hbm": T * d * (2 + 4 + 4 + 2) / (ms * 1e-3) / hbm}
+            # feed-forwards over T tokens
+            ms = _timed(lambda: lef.blocks[1].mlp(x), iters, flush)
+            kern["experts_lefalix"] = {"ms": ms, "frac_of_measured_bf16": 6.0 * T * top * ff * d / (ms * 1e-3) / tf}
+            ms = _timed(lambda: pom.blocks[0].mlp(x), iters, flush)
+            kern["experts_pomipel"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * top * ff * d / (ms * 1e-3) / tf}
+            ms = _timed(lambda: lef.blocks[0].mlp(x), iters, flush)
+            kern["dense_mlp_lefalix"] = {"ms": ms, "frac_of_measured_bf16": 4.0 * T * dff * d / (ms * 1e-3) / tf}
+            res["kernels"] = {k: {a: (round(b, 4) if isinstance(b, float) else b) for a, b in v.items()} for k, v in kern.items()}
+        out[name] = res
+        del lef, pom
+        torch.cuda.empty_cache()
+    print(json.dumps({"compare": "lefalix", "layers": 4, "prompt": T, "context": T, "dtype": "bf16", "data": "synthetic, random weights",
+                      "l2": "flushed between timed calls", "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                                                                       "source": peak_source},
+                      "gpu_launches": int(K.launch_count() - launches0), "sizes": out}), flush=True)
+
+
 def main() -> None:
     # stdout carries exactly one JSON line: NCCL's own banner / debug lines (when the box sets NCCL_DEBUG) go to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
@@ -631,11 +793,14 @@ def main() -> None:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama2-7b-nf4-bs1")
     ap.add_argument("--layers", type=int, default=None, help="debug only: build fewer blocks (invalidates the number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--compare", choices=["pomipel"], default=None,
+    ap.add_argument("--compare", choices=["pomipel", "lefalix"], default=None,
                     help="instead of the default workload: prefill / decode throughput of that design beside the closest existing model")
-    ap.add_argument("--sizes", default=None, help=f"--compare: comma-separated subset of {sorted(ARCH_SIZES)}")
+    ap.add_argument("--sizes", default=None, help=f"--compare: comma-separated subset of {sorted(ARCH_SIZES)} (the same names for both designs)")
     ap.add_argument("--prompt", type=int, default=2048, help="--compare: prompt and context length")
     args = ap.parse_args()
+    if args.compare == "lefalix":
+        run_lefalix_compare(args)
+        return
     if args.compare:
         run_arch_compare(args)
         return

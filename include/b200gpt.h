@@ -442,6 +442,13 @@ int b200_moe_gemv(const void* x, const int32_t* ids, const float* weights, const
 int b200_moe_combine(const void* y, const int32_t* slot_of, const float* weights, void* out, int64_t tokens, int top, int d, int dtype,
                      b200_stream_t stream);
 
+/* The tensor-core tiles of b200_attn_prefill for sequences that start in this step (every seqs[b] at position 0): bf16, dk = dv =
+ * head_size in {64, 128}, grouped key-value heads, a sliding window (0: none) and per-head sink logits (NULL: none).  k and v are
+ * the step's own rows (rows, n_kv_head * head_size). */
+int b200_attn_prefill_window(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
+                             int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size, float scale,
+                             int window, const void* sink, b200_stream_t stream);
+
 /* ---- sequence-state mechanisms: short convolutions, the gated delta rule, windowed attention over a ring -------------------
  * A step's rows are the new tokens of several sequences packed one after another; seqs[s] = {first row, rows, position of the
  * first row, state slot} (int32[n_seqs][4], 16-byte aligned) and row_seq[row] = s. */

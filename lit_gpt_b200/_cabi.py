@@ -156,6 +156,8 @@ _CORE_SIGNATURES = {
                                      c_void_p]),
     "b200_window_attn": (c_int, [ctypes.POINTER(WindowAttnArgs), c_void_p]),
     "b200_window_attn_tune": (c_int, [c_int]),
+    "b200_attn_prefill_window": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int,
+                                         c_int, c_float, c_int, c_void_p, c_void_p]),
     "b200_ring_store": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_int,
                                 c_void_p]),
 }

@@ -30,6 +30,12 @@ struct PfView {
   int64_t v_b, v_h, v_r;
   int64_t y_b, y_r;
   const int4* seqs;
+  // ragged only.  window > 0: row at position i sees keys i - window < j <= i.  sink: one logit per head that joins the softmax
+  // denominator (no key, no value, not scaled).  kv_first_row: the sequences start at position 0 and k / v hold exactly the
+  // step's rows, so a sequence's keys start at its first query row (seqs[b].w is then free for the caller's own use).
+  int window;
+  const __nv_bfloat16* sink;
+  int kv_first_row;
 };
 
 template <int HS, typename PosT>
@@ -60,7 +66,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     pos0 = sq.z;
     max_seq = sq.z + sq.y;
     qrow0 = sq.x;
-    kvrow0 = sq.w;
+    kvrow0 = vw.kv_first_row ? sq.x : sq.w;
     if (r0 >= T) return;
   }
 
@@ -93,6 +99,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
   for (int w = 0; w < kPfThreads / 32; ++w) cta_lim = max(cta_lim, s_maxpos[w]);
   const int ntiles = (cta_lim + kPfBN) / kPfBN;      // cta_lim >= 0 because r0 < T
+  const int window = vw.seqs ? vw.window : 0;
+  // with a window the first rows of the tile decide where the key range starts (ragged positions grow with the row)
+  const int tile_lo = window > 0 ? max(0, pos0 + r0 - window + 1) / kPfBN : 0;
+  const int loA = window > 0 ? limA - window + 1 : 0, loB = window > 0 ? limB - window + 1 : 0;
+  const int warp_lo = window > 0 ? pos0 + r0 + warp * 16 - window + 1 : 0;     // lowest key any row of this warp sees
 
   auto load_kv = [&](int tile, int buf) {
     const int j0 = tile * kPfBN;
@@ -105,7 +116,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     }
     pf_commit();
   };
-  load_kv(0, 0);
+  load_kv(tile_lo, tile_lo & 1);
 
   float o_acc[HS / 8][4];
 #pragma unroll
@@ -121,12 +132,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     ldsm_x4(qf[ks], pf_smem(sQ) + sw<HS>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
 
   const int warp_lim = wl;
-  for (int tile = 0; tile < ntiles; ++tile) {
+  for (int tile = tile_lo; tile < ntiles; ++tile) {
     const int buf = tile & 1;
     if (tile + 1 < ntiles) { load_kv(tile + 1, buf ^ 1); pf_wait<1>(); } else { pf_wait<0>(); }
     __syncthreads();
     const int j0 = tile * kPfBN;
-    if (j0 <= warp_lim) {   // warp-uniform: tiles entirely above this warp's rows contribute nothing
+    if (j0 <= warp_lim && j0 + kPfBN > warp_lo) {   // warp-uniform: tiles entirely above this warp's rows, or below their windows, contribute nothing
       float s[kPfBN / 8][4];
 #pragma unroll
       for (int i = 0; i < kPfBN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -142,16 +153,17 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         }
       }
       // causal limit + running maximum
-      const bool need_mask = j0 + kPfBN - 1 > min(limA < 0 ? 0x7fffffff : limA, limB < 0 ? 0x7fffffff : limB) || limA < 0 || limB < 0;
+      const bool need_mask = j0 + kPfBN - 1 > min(limA < 0 ? 0x7fffffff : limA, limB < 0 ? 0x7fffffff : limB) || limA < 0 || limB < 0 ||
+                             (window > 0 && j0 < max(loA, loB));
       float tmA = -INFINITY, tmB = -INFINITY;
 #pragma unroll
       for (int i = 0; i < kPfBN / 8; ++i) {
         if (need_mask) {
           const int j = j0 + i * 8 + 2 * tq;
-          if (j > limA) s[i][0] = -INFINITY;
-          if (j + 1 > limA) s[i][1] = -INFINITY;
-          if (j > limB) s[i][2] = -INFINITY;
-          if (j + 1 > limB) s[i][3] = -INFINITY;
+          if (j > limA || j < loA) s[i][0] = -INFINITY;
+          if (j + 1 > limA || j + 1 < loA) s[i][1] = -INFINITY;
+          if (j > limB || j < loB) s[i][2] = -INFINITY;
+          if (j + 1 > limB || j + 1 < loB) s[i][3] = -INFINITY;
         }
         tmA = fmaxf(tmA, fmaxf(s[i][0], s[i][1]));
         tmB = fmaxf(tmB, fmaxf(s[i][2], s[i][3]));
@@ -192,7 +204,14 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
   lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
   lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
-  const float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
+  float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
+  if (vw.seqs && vw.sink) {   // the sink joins the denominator once: l is in units of exp2(m * scale_log2)
+    const float sk = __bfloat162float(vw.sink[h]) * 1.4426950408889634f;
+    const float eA = mA == -INFINITY ? sk : fmaxf(mA * scale_log2, sk), eB = mB == -INFINITY ? sk : fmaxf(mB * scale_log2, sk);
+    const float cA = mA == -INFINITY ? 0.f : exp2f(mA * scale_log2 - eA), cB = mB == -INFINITY ? 0.f : exp2f(mB * scale_log2 - eB);
+    iA = cA / (lA * cA + exp2f(sk - eA));
+    iB = cB / (lB * cB + exp2f(sk - eB));
+  }
   if (rowA < T) {
     __nv_bfloat16* yr = y + (int64_t)b * vw.y_b + (qrow0 + rowA) * vw.y_r + (int64_t)h * HS;
 #pragma unroll
@@ -211,7 +230,7 @@ cudaError_t launch_prefill(const void* q, const void* kc, const void* vc, const 
   // default: q (B, H, T, HS), caches (B, G, max_seq, HS), y (B, T, H * HS)
   const PfView vw = view ? *view
                          : PfView{(int64_t)H * T * HS, (int64_t)T * HS, HS, (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS,
-                                  (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr};
+                                  (int64_t)G * max_seq * HS, (int64_t)max_seq * HS, HS, (int64_t)T * H * HS, (int64_t)H * HS, nullptr, 0, nullptr, 0};
   const size_t smem = (size_t)(kPfBM + 4 * kPfBN) * HS * 2;
   static PerDeviceOnce once;
   if (once.need()) {
@@ -259,9 +278,29 @@ extern "C" int b200_attn_prefill_ragged(const void* q, int64_t ldq, const void* 
   B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0, "b200_attn_prefill_ragged: leading dimensions must be multiples of 8 elements");
   B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_ragged: operands must be 16-byte aligned");
-  const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs)};
+  const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), 0, nullptr, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
   else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_head, 0, scale, st, &vw)));
+  return B200_OK;
+}
+
+// The same tiles for sequences that START in this step (every seqs[b] at position 0): sliding window, sink logits and grouped
+// key-value heads; q (rows, H * hs), k and v (rows, G * hs) are the step's own packed rows, seqs[b] = {first row, rows, 0, any}.
+extern "C" int b200_attn_prefill_window(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const int32_t* seqs,
+                                        int n_seqs, int max_q_len, void* y, int64_t ldy, int n_head, int n_kv_head, int head_size, float scale,
+                                        int window, const void* sink, b200_stream_t stream) {
+  B200_CHECK_ARG(q && k && v && seqs && y, "b200_attn_prefill_window: null pointer");
+  B200_CHECK_ARG(n_seqs > 0 && n_seqs <= 65535 && max_q_len > 0 && n_head > 0 && n_head <= 65535 && n_kv_head > 0 && n_head % n_kv_head == 0 &&
+                 window >= 0, "b200_attn_prefill_window: bad shape");
+  B200_CHECK_ARG(head_size == 64 || head_size == 128, "b200_attn_prefill_window: head_size must be 64 or 128 (got %d)", head_size);
+  B200_CHECK_ARG(((ldq | ldk | ldv) & 7) == 0 && (ldy & 1) == 0, "b200_attn_prefill_window: leading dimensions must be multiples of 8 elements");
+  B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(seqs)) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(y) & 3) == 0, "b200_attn_prefill_window: operands must be 16-byte aligned");
+  const PfView vw{0, head_size, ldq, 0, head_size, ldk, 0, head_size, ldv, 0, ldy, reinterpret_cast<const int4*>(seqs), window,
+                  reinterpret_cast<const __nv_bfloat16*>(sink), 1};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (head_size == 128) B200_CUDA((launch_prefill<128, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
+  else B200_CUDA((launch_prefill<64, int32_t>(q, k, v, nullptr, y, n_seqs, max_q_len, n_head, n_kv_head, 0, scale, st, &vw)));
   return B200_OK;
 }

@@ -903,11 +903,16 @@ def gated_rms_heads(o: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, head
     return out
 
 
+WINDOW_PREFILL_MMA = True   # tests switch it off to run whole prompts with tensor-core-sized heads on the any-size kernel
+
+
 def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch.Tensor, v_ring: torch.Tensor, sink: Optional[torch.Tensor],
                 seqs: torch.Tensor, row_seq: torch.Tensor, max_q_len: int, n_head: int, n_kv_head: int, dk: int, dv: int, window: int,
-                scale: float) -> torch.Tensor:
+                scale: float, from_start: bool = False) -> torch.Tensor:
     """Sliding-window attention with a sink over this step's k / v rows and the rings (slots, ring, G * dk | dv) of earlier
-    positions; afterwards the step's rows enter the rings.  -> (n, n_head * dv)"""
+    positions; afterwards the step's rows enter the rings.  -> (n, n_head * dv).  from_start: every sequence of the step begins
+    at position 0, so nothing is read from the rings -- bf16 prompts with 64- or 128-wide heads then run on the tensor-core tiles
+    of the prefill kernel the other models use."""
     C.require_cuda(q, k, v, k_ring, v_ring, sink, seqs, row_seq)
     if not (q.dtype == k.dtype == v.dtype == k_ring.dtype == v_ring.dtype) or not (k_ring.is_contiguous() and v_ring.is_contiguous()):
         raise C.B200Error("window_attn: one dtype, contiguous rings")
@@ -916,14 +921,24 @@ def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch
     ring = k_ring.shape[1]
     out = torch.empty((q.shape[0], n_head * dv), dtype=q.dtype, device=q.device)
     lib, st = C.load_core(), C.stream_ptr(q.device)
+    if (from_start and max_q_len > 1 and WINDOW_PREFILL_MMA and q.dtype == torch.bfloat16 and dk == dv and dk in (64, 128)
+            and not (q.stride(0) | k.stride(0) | v.stride(0)) & 7 and not (q.data_ptr() | k.data_ptr() | v.data_ptr() | seqs.data_ptr()) & 15):
+        C.check(lib.b200_attn_prefill_window(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), seqs.data_ptr(),
+                                             seqs.shape[0], max_q_len, out.data_ptr(), out.stride(0), n_head, n_kv_head, dk, float(scale), window,
+                                             C.ptr(sink), st), "attn_prefill_window")
+    else:
+        _window_attn_any(lib, st, q, k, v, out, k_ring, v_ring, sink, seqs, max_q_len, ring, n_head, n_kv_head, dk, dv, window, scale)
+    C.check(lib.b200_ring_store(k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_ring.data_ptr(), v_ring.data_ptr(), ring, n_kv_head * dk,
+                                n_kv_head * dv, seqs.data_ptr(), row_seq.data_ptr(), q.shape[0], _code(q), st), "ring_store")
+    return out
+
+
+def _window_attn_any(lib, st, q, k, v, out, k_ring, v_ring, sink, seqs, max_q_len, ring, n_head, n_kv_head, dk, dv, window, scale) -> None:
     args = C.WindowAttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
                             ldo=out.stride(0), k_ring=k_ring.data_ptr(), v_ring=v_ring.data_ptr(), sink=C.ptr(sink), seqs=seqs.data_ptr(),
                             n_seqs=seqs.shape[0], max_q_len=max_q_len, ring=ring, n_head=n_head, n_kv_head=n_kv_head, dk=dk, dv=dv, window=window,
                             scale=float(scale), dtype=_code(q))
     C.check(lib.b200_window_attn(ctypes.byref(args), st), "window_attn")
-    C.check(lib.b200_ring_store(k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_ring.data_ptr(), v_ring.data_ptr(), ring, n_kv_head * dk,
-                                n_kv_head * dv, seqs.data_ptr(), row_seq.data_ptr(), q.shape[0], _code(q), st), "ring_store")
-    return out
 
 
 def window_attn_tune(force_tiled_kernel: bool = False) -> bool:

@@ -42,7 +42,7 @@ def state_batch(seqs: Sequence[Tuple[int, int, int]], device: torch.device, extr
     i32 = torch.tensor(meta + row_seq + [int(v) for v in extra], dtype=torch.int32).to(device, non_blocking=True)
     batch = RaggedBatch(row_pos=None, row_slot=None, cache_rows=None, decode=all(s[2] == 1 for s in seqs),
                         context_hint=max(s[1] + s[2] for s in seqs), max_q_len=max(s[2] for s in seqs),
-                        seq_state=i32[: 4 * S].view(S, 4), row_seq=i32[4 * S : 4 * S + first])
+                        seq_state=i32[: 4 * S].view(S, 4), row_seq=i32[4 * S : 4 * S + first], identity_ctx=all(s[1] == 0 for s in seqs))
     return batch, i32[4 * S + first :]
 
 

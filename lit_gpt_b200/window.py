@@ -85,5 +85,5 @@ class WindowAttention(nn.Module):
         ]
         K.short_conv(qkv, groups, s.conv, state.tail, batch.seq_state, batch.row_seq)
         y = K.window_attn(q, k, v, state.k_ring, state.v_ring, self.sink, batch.seq_state, batch.row_seq, batch.max_q_len, H, G, dk, dv,
-                          s.window, s.scale)
+                          s.window, s.scale, from_start=batch.identity_ctx)
         return F.linear(y, self.w_o, self.b_o)

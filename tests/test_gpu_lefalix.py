@@ -166,14 +166,14 @@ TOL = {torch.float32: 3e-5, torch.bfloat16: 8e-2}
 
 def assert_close(got, want, dtype, what=""):
     """fp32: the whole block within rounding.  bf16: a rounding difference ahead of a router can move a token to another expert
-    (in exact arithmetic on bf16-rounded inputs just as well), so the typical row and nine rows in ten must be within bf16
-    rounding; the fp32 runs of the same tests are the sharp ones."""
+    (in exact arithmetic on bf16-rounded inputs just as well), so the typical row and four rows in five must be within bf16
+    rounding (these models are a few dozen channels wide, so one moved token is a large share of a row); the fp32 runs of the same tests are the sharp ones."""
     if dtype == torch.float32:
         assert rel_err(got, want) < TOL[dtype], (what, rel_err(got, want))
         return
     got, want = got.double().cpu(), want.double().cpu()
     rows = (got - want).norm(dim=-1) / want.norm(dim=-1).clamp_min(1e-30)
-    assert float(rows.median()) < 4e-2 and float((rows < TOL[dtype]).double().mean()) >= 0.9, (what, rows)
+    assert float(rows.median()) < 4e-2 and float((rows < TOL[dtype]).double().mean()) >= 0.8, (what, rows)
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -266,6 +266,63 @@ def test_window_edge_is_exact_in_prompt_and_decoding():
             finally:
                 k.window_attn_tune(force_tiled_kernel=old)
             assert rel_err(torch.cat(got), want) < 1e-5, (cuts, tiled)
+
+
+def _windowed_softmax(q, kk, v, sink, H, G, dk, dv, size, scale):
+    """float64 attention of one sequence from position 0: q (n, H dk), kk (n, G dk), v (n, G dv)."""
+    n = q.shape[0]
+    q, kk, v = q.double().view(n, H, dk), kk.double().view(n, G, dk), v.double().view(n, G, dv)
+    out = torch.zeros(n, H, dv, dtype=torch.float64)
+    for i in range(n):
+        lo = max(0, i - size + 1)
+        for hh in range(H):
+            g = hh // (H // G)
+            s = (kk[lo : i + 1, g] @ q[i, hh]) * scale
+            e = torch.exp(s - s.max())
+            out[i, hh] = (e / (e.sum() + torch.exp(sink[hh].double() - s.max()))) @ v[lo : i + 1, g]
+    return out.reshape(n, H * dv)
+
+
+@pytest.mark.parametrize("hs,size", [(64, 100), (64, 64), (128, 1), (128, 150), (64, 1000)])
+def test_window_prefill_on_the_tensor_cores(hs, size):
+    """bf16 prompts with 64- / 128-wide heads take the tensor-core tiles: windows that end inside a key tile, at its edge, of one
+    position and longer than the prompt; grouped heads; three sequences of unequal length in one launch (one shorter than a
+    query tile, one spanning several).  Compared with exact attention on the same bf16 operands and with the any-size kernel."""
+    k = K()
+    from lit_gpt_b200.ragged import state_batch
+
+    H, G = 4, 2
+    g = torch.Generator().manual_seed(hs + size)
+    lens = [200, 37, 300]
+    n = sum(lens)
+    q = torch.randn(n, H * hs, generator=g).to(torch.bfloat16)
+    kk = torch.randn(n, G * hs, generator=g).to(torch.bfloat16)
+    v = torch.randn(n, G * hs, generator=g).to(torch.bfloat16)
+    sink = torch.tensor([0.5, -1.0, 2.0, 0.0]).to(torch.bfloat16)
+    scale = 2.0 * hs ** -0.5           # sharp: the few largest scores carry the row
+    want, at = [], 0
+    for ln in lens:
+        want.append(_windowed_softmax(q[at : at + ln], kk[at : at + ln], v[at : at + ln], sink.float(), H, G, hs, hs, size, scale))
+        at += ln
+    want = torch.cat(want)
+    batch, _ = state_batch([(0, 0, lens[0]), (2, 0, lens[1]), (1, 0, lens[2])], torch.device("cuda"))
+    assert batch.identity_ctx
+    ring = min(size, 400)
+    outs = {}
+    for mma in (True, False):
+        k.WINDOW_PREFILL_MMA = mma
+        try:
+            k_ring, v_ring = torch.zeros(3, ring, G * hs, dtype=torch.bfloat16, device="cuda"), torch.zeros(3, ring, G * hs, dtype=torch.bfloat16, device="cuda")
+            launches = k.launch_count()
+            outs[mma] = k.window_attn(q.cuda(), kk.cuda(), v.cuda(), k_ring, v_ring, sink.cuda(), batch.seq_state, batch.row_seq, max(lens), H, G, hs, hs,
+                                      min(size, ring), scale, from_start=True).float().cpu()
+            assert k.launch_count() - launches == 2
+        finally:
+            k.WINDOW_PREFILL_MMA = True
+        # the rings hold every sequence's last positions whichever kernel ran
+        last = lens[2] - 1
+        assert torch.equal(k_ring[1, last % ring].cpu(), kk[lens[0] + lens[1] + last]) and torch.equal(v_ring[2, (lens[1] - 1) % ring].cpu(), v[lens[0] + lens[1] - 1])
+    assert rel_err(outs[False], want) < 6e-3 and rel_err(outs[True], want) < 1.2e-2, (rel_err(outs[False], want), rel_err(outs[True], want))
 
 
 def test_sink_takes_probability_once_and_unscaled():
