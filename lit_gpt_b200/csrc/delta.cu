@@ -9,7 +9,8 @@
 // The columns of S never mix: column j evolves from (k, q, g, beta) and v[j] alone.  So the work of one (sequence, head) is
 // split over columns -- a group of LPC lanes owns one column, each lane holding dk / LPC of its numbers in registers -- and
 // over CTAs (column blocks).  Time is walked in order: tiles of tokens are staged in shared memory (keys, queries, decays
-// already turned into g), then every lane group does two short dot products and two updates per token.  One kernel serves
+// already turned into g) while the previous tile is walked; per token every lane group does three short dot products that
+// share one reduction (o = (g S)^T q + (k . q) u needs no second pass over the updated state) and one update.  One kernel serves
 // prompts (many rows per sequence) and decoding (one row: the cost is reading and writing S once).
 //
 // A sequence that starts at position 0 starts from S = 0 whatever its slot holds.  The state is stored in the order the
@@ -48,6 +49,8 @@ __global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A) {
   constexpr int TT = 64 / LPC;                 // tokens per staged tile
   constexpr int DKP = kDrKPL * LPC;            // padded key size
   constexpr int COLS = kDrThreads / LPC;       // columns per CTA
+  constexpr int NIT = TT * DKP / kDrThreads;   // key elements of a tile per thread (8)
+  constexpr int NV = (TT * COLS + kDrThreads - 1) / kDrThreads;   // value elements of a tile per thread
   extern __shared__ __align__(16) float dr_smem[];
   float* const ks = dr_smem;                   // [TT][DKP]
   float* const qs = ks + TT * DKP;             // [TT][DKP]
@@ -75,71 +78,106 @@ __global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A) {
   const T* const dec = reinterpret_cast<const T*>(A.decay_in);
   const T* const bet = reinterpret_cast<const T*>(A.beta_in);
 
-  for (int t0 = 0; t0 < len; t0 += TT) {
-    const int nt = min(TT, len - t0);
-    __syncthreads();
-    for (int idx = tid; idx < TT * DKP; idx += kDrThreads) {
-      const int t = idx / DKP, i = idx - t * DKP;
-      float kv = 0.f, qv = 0.f, gv = 1.f;
-      if (t < nt && i < dk) {
-        const int64_t row = first + t0 + t;
-        kv = A.k[row * A.ldk + (int64_t)hk * dk + i];
-        qv = A.q[row * A.ldq + (int64_t)hk * dk + i];
-        if (CHANNEL) gv = expf(neg_a * softplus_f(load_as_float(dec, row * A.ld_decay + (int64_t)h * dk + i) + load_as_float(bias, (int64_t)h * dk + i)));
-      }
-      ks[idx] = kv;
-      qs[idx] = qv;
-      if (CHANNEL) gs[idx] = gv;
+  // A tile's inputs travel global -> registers -> shared memory: the loads of tile n + 1 are issued before the tokens of tile n
+  // are walked, so their latency hides behind the recurrence; the decays are turned into g on the way into shared memory.
+  float rk[NIT], rq[NIT], rd[CHANNEL ? NIT : 1], rbias[CHANNEL ? NIT : 1], rv[NV], rb = 0.f, rg = 0.f;
+  if (CHANNEL) {
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int i = (tid + it * kDrThreads) % DKP;
+      rbias[it] = i < dk ? load_as_float(bias, (int64_t)h * dk + i) : 0.f;
     }
-    for (int idx = tid; idx < TT * COLS; idx += kDrThreads) {
-      const int t = idx / COLS, c = (int)blockIdx.x * COLS + (idx - t * COLS);
-      vs[idx] = (t < nt && c < dv) ? A.v[(int64_t)(first + t0 + t) * A.ldv + (int64_t)h * dv + c] : 0.f;
+  }
+  const float hbias = CHANNEL ? 0.f : load_as_float(bias, h);
+  auto load_tile = [&](int t0) {
+    const int nt = min(TT, len - t0);
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int idx = tid + it * kDrThreads, t = idx / DKP, i = idx - t * DKP;
+      const bool ok = t < nt && i < dk;
+      const int64_t row = first + t0 + t;
+      rk[it] = ok ? A.k[row * A.ldk + (int64_t)hk * dk + i] : 0.f;
+      rq[it] = ok ? A.q[row * A.ldq + (int64_t)hk * dk + i] : 0.f;
+      if (CHANNEL) rd[it] = ok ? load_as_float(dec, row * A.ld_decay + (int64_t)h * dk + i) : 0.f;
+    }
+#pragma unroll
+    for (int iv = 0; iv < NV; ++iv) {
+      const int idx = tid + iv * kDrThreads, t = idx / COLS, c = (int)blockIdx.x * COLS + (idx - t * COLS);
+      rv[iv] = (idx < TT * COLS && t < nt && c < dv) ? A.v[(int64_t)(first + t0 + t) * A.ldv + (int64_t)h * dv + c] : 0.f;
     }
     if (tid < TT) {
-      float b = 0.f, g = 1.f;
-      if (tid < nt) {
-        const int64_t row = first + t0 + tid;
-        b = 1.0f / (1.0f + expf(-load_as_float(bet, row * A.ld_beta + h)));
-        if (!CHANNEL) g = expf(neg_a * softplus_f(load_as_float(dec, row * A.ld_decay + h) + load_as_float(bias, h)));
-      }
-      bs[tid] = b;
-      if (!CHANNEL) gs[tid] = g;
+      const bool ok = tid < nt;
+      const int64_t row = first + t0 + tid;
+      rb = ok ? load_as_float(bet, row * A.ld_beta + h) : -INFINITY;
+      if (!CHANNEL) rg = ok ? load_as_float(dec, row * A.ld_decay + h) : 0.f;
     }
+  };
+  auto store_tile = [&]() {
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int idx = tid + it * kDrThreads;
+      ks[idx] = rk[it];
+      qs[idx] = rq[it];
+      if (CHANNEL) gs[idx] = expf(neg_a * softplus_f(rd[it] + rbias[it]));
+    }
+#pragma unroll
+    for (int iv = 0; iv < NV; ++iv) {
+      const int idx = tid + iv * kDrThreads;
+      if (idx < TT * COLS) vs[idx] = rv[iv];
+    }
+    if (tid < TT) {
+      bs[tid] = 1.0f / (1.0f + expf(-rb));
+      if (!CHANNEL) gs[tid] = expf(neg_a * softplus_f(rg + hbias));
+    }
+  };
+
+  load_tile(0);
+  for (int t0 = 0; t0 < len; t0 += TT) {
+    const int nt = min(TT, len - t0);
+    __syncthreads();                       // the previous tile's tokens are done with shared memory
+    store_tile();
     __syncthreads();
+    if (t0 + TT < len) load_tile(t0 + TT);
     for (int t = 0; t < nt; ++t) {
       const float* kt = ks + t * DKP + sub;
       const float* qt = qs + t * DKP + sub;
+      // with D = g S (decayed state):  u = beta (v - D^T k),  S = D + k u^T,  o = S^T q = D^T q + (k . q) u
+      // so the three dot products over the key axis are independent and share the rounds of one reduction
       float kr[kDrKPL];
-      float dot = 0.f;
+      float dk_ = 0.f, dq_ = 0.f, kq_ = 0.f;
       if (CHANNEL) {
         const float* gt = gs + t * DKP + sub;
 #pragma unroll
         for (int r = 0; r < kDrKPL; ++r) {
           kr[r] = kt[r * LPC];
+          const float qv = qt[r * LPC];
           S[r] *= gt[r * LPC];
-          dot = fmaf(S[r], kr[r], dot);
+          dk_ = fmaf(S[r], kr[r], dk_);
+          dq_ = fmaf(S[r], qv, dq_);
+          kq_ = fmaf(kr[r], qv, kq_);
         }
       } else {
         const float g = gs[t];
 #pragma unroll
         for (int r = 0; r < kDrKPL; ++r) {
           kr[r] = kt[r * LPC];
+          const float qv = qt[r * LPC];
           S[r] *= g;
-          dot = fmaf(S[r], kr[r], dot);
+          dk_ = fmaf(S[r], kr[r], dk_);
+          dq_ = fmaf(S[r], qv, dq_);
+          kq_ = fmaf(kr[r], qv, kq_);
         }
       }
 #pragma unroll
-      for (int o = LPC / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = bs[t] * (vs[t * COLS + cl] - dot);
-      float od = 0.f;
-#pragma unroll
-      for (int r = 0; r < kDrKPL; ++r) {
-        S[r] = fmaf(kr[r], u, S[r]);
-        od = fmaf(S[r], qt[r * LPC], od);
+      for (int o = LPC / 2; o > 0; o >>= 1) {
+        dk_ += __shfl_xor_sync(0xffffffffu, dk_, o);
+        dq_ += __shfl_xor_sync(0xffffffffu, dq_, o);
+        kq_ += __shfl_xor_sync(0xffffffffu, kq_, o);
       }
+      const float u = bs[t] * (vs[t * COLS + cl] - dk_);
 #pragma unroll
-      for (int o = LPC / 2; o > 0; o >>= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
-      if (sub == 0 && col_ok) A.out[(int64_t)(first + t0 + t) * A.ldo + (int64_t)h * dv + col] = od;
+      for (int r = 0; r < kDrKPL; ++r) S[r] = fmaf(kr[r], u, S[r]);
+      if (sub == 0 && col_ok) A.out[(int64_t)(first + t0 + t) * A.ldo + (int64_t)h * dv + col] = fmaf(kq_, u, dq_);
     }
   }
   if (col_ok) {

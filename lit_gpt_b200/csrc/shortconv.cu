@@ -38,10 +38,37 @@ struct CvParams {
   int n_groups, taps, total_heads;
 };
 
+// two neighbouring elements at once when the caller vouches for the alignment (one 4- or 8-byte access)
 template <typename T>
+__device__ __forceinline__ void load_pair(const T* p, int64_t i, bool pair, bool second, float& a, float& b);
+template <>
+__device__ __forceinline__ void load_pair<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i, bool pair, bool second, float& a, float& b) {
+  if (pair) {
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(p + i);
+    a = bf16lo(v);
+    b = bf16hi(v);
+  } else {
+    a = __bfloat162float(p[i]);
+    b = second ? __bfloat162float(p[i + 1]) : 0.f;
+  }
+}
+template <>
+__device__ __forceinline__ void load_pair<float>(const float* p, int64_t i, bool pair, bool second, float& a, float& b) {
+  if (pair) {
+    const float2 v = *reinterpret_cast<const float2*>(p + i);
+    a = v.x;
+    b = v.y;
+  } else {
+    a = p[i];
+    b = second ? p[i + 1] : 0.f;
+  }
+}
+
+// NIT: 64-element pieces of the widest head; TAPS: the number of taps when it is one of the unrolled ones, else 0 (read at run time)
+template <typename T, int NIT, int TAPS>
 __global__ void __launch_bounds__(kCvThreads) short_conv_kernel(const T* __restrict__ in, int64_t ld_in, CvParams P,
                                                                  const T* __restrict__ tail, int64_t tail_slot_stride, int tail_cols,
-                                                                 const int4* __restrict__ seqs, const int* __restrict__ row_seq) {
+                                                                 const int4* __restrict__ seqs, const int* __restrict__ row_seq, int pairs) {
   griddep_launch();
   griddep_wait();
   const int lane = threadIdx.x & 31;
@@ -54,38 +81,45 @@ __global__ void __launch_bounds__(kCvThreads) short_conv_kernel(const T* __restr
   const int4 sq = seqs[row_seq[row]];
   const int r = (int)(row - sq.x);            // row within the step's part of its sequence
   const int pos = sq.z + r;
-  const int taps = P.taps;
+  const int taps = TAPS ? TAPS : P.taps;
   const T* tl = tail + (int64_t)sq.w * tail_slot_stride;
   const T* wt = reinterpret_cast<const T*>(G.w);
   const int c_head = G.col0 + hh * G.dim;     // first channel of this head among the convolved columns
+  const bool pair = pairs != 0;
 
-  float val[kCvMaxIt][2];
+  float val[NIT][2];
   float ss = 0.f;
 #pragma unroll
-  for (int it = 0; it < kCvMaxIt; ++it) {
+  for (int it = 0; it < NIT; ++it) {
+    const int d = it * 64 + lane * 2;
+    float acc0 = 0.f, acc1 = 0.f;
+    if (d < G.dim) {
+      const bool second = d + 1 < G.dim;
+      const int c = c_head + d;
+      const T* wc = wt + (int64_t)(hh * G.dim + d) * taps;
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int d = it * 64 + lane * 2 + e;
-      float acc = 0.f;
-      if (d < G.dim) {
-        const int c = c_head + d;
-        const T* wc = wt + (int64_t)(hh * G.dim + d) * taps;
-        for (int j = 0; j < taps; ++j) {
-          const int back = taps - 1 - j;       // how many positions before this row
-          if (back > pos) continue;            // before the sequence's first token: zero
-          float u;
-          if (back <= r) u = load_as_float(in, (row - back) * ld_in + c);
-          else u = load_as_float(tl, (int64_t)(taps - 1 - (back - r)) * tail_cols + c);   // tail row taps-1-k holds the k-th row before the step
-          acc = fmaf(load_as_float(wc, j), u, acc);
+      for (int j = 0; j < (TAPS ? TAPS : kCvMaxTaps + 1); ++j) {
+        if (!TAPS && j >= taps) break;
+        const int back = taps - 1 - j;       // how many positions before this row
+        float u0 = 0.f, u1 = 0.f;
+        if (back <= pos) {                   // else: before the sequence's first token, zero
+          if (back <= r) load_pair(in, (row - back) * ld_in + c, pair, second, u0, u1);
+          else load_pair(tl, (int64_t)(taps - 1 - (back - r)) * tail_cols + c, pair, second, u0, u1);   // tail row taps-1-k: the k-th row before the step
         }
-        if (G.act == 1) acc = acc / (1.0f + expf(-acc));
+        acc0 = fmaf(load_as_float(wc, j), u0, acc0);
+        if (second) acc1 = fmaf(load_as_float(wc, taps + j), u1, acc1);
       }
-      val[it][e] = acc;
+      if (G.act == 1) {
+        acc0 = acc0 / (1.0f + expf(-acc0));
+        acc1 = acc1 / (1.0f + expf(-acc1));
+      }
     }
+    val[it][0] = acc0;
+    val[it][1] = acc1;
   }
   if (G.post == 1) {
 #pragma unroll
-    for (int it = 0; it < kCvMaxIt; ++it) {
+    for (int it = 0; it < NIT; ++it) {
       const int d = it * 64 + lane * 2;
       if (d + 1 < G.rot_dims && d + 1 < G.dim) {
         // the angle in double, reduced to [-pi, pi] before the fp32 sine and cosine: exact to fp32 at any position
@@ -103,14 +137,14 @@ __global__ void __launch_bounds__(kCvThreads) short_conv_kernel(const T* __restr
   }
   if (G.post != 0) {
 #pragma unroll
-    for (int it = 0; it < kCvMaxIt; ++it) ss += val[it][0] * val[it][0] + val[it][1] * val[it][1];   // lanes past dim hold zeros
+    for (int it = 0; it < NIT; ++it) ss += val[it][0] * val[it][0] + val[it][1] * val[it][1];   // lanes past dim hold zeros
     ss = warp_sum(ss);
   }
   float mul = G.post_scale;
   if (G.post == 1) mul *= 1.0f / sqrtf(ss / (float)G.dim + G.eps);
   else if (G.post == 2) mul *= 1.0f / sqrtf(ss + G.eps);
 #pragma unroll
-  for (int it = 0; it < kCvMaxIt; ++it) {
+  for (int it = 0; it < NIT; ++it) {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int d = it * 64 + lane * 2 + e;
@@ -120,6 +154,17 @@ __global__ void __launch_bounds__(kCvThreads) short_conv_kernel(const T* __restr
         else store_from_float(reinterpret_cast<T*>(G.out), o, val[it][e] * mul);
       }
     }
+  }
+}
+
+template <typename T, int NIT>
+cudaError_t short_conv_launch(int taps, dim3 grid, cudaStream_t st, const T* in, int64_t ld_in, const CvParams& P, const T* tail,
+                              int64_t tail_slot_stride, int tail_cols, const int4* seqs, const int* row_seq, int pairs) {
+  switch (taps) {
+    case 2: return launch(short_conv_kernel<T, NIT, 2>, grid, dim3(kCvThreads), 0, st, in, ld_in, P, tail, tail_slot_stride, tail_cols, seqs, row_seq, pairs);
+    case 3: return launch(short_conv_kernel<T, NIT, 3>, grid, dim3(kCvThreads), 0, st, in, ld_in, P, tail, tail_slot_stride, tail_cols, seqs, row_seq, pairs);
+    case 4: return launch(short_conv_kernel<T, NIT, 4>, grid, dim3(kCvThreads), 0, st, in, ld_in, P, tail, tail_slot_stride, tail_cols, seqs, row_seq, pairs);
+    default: return launch(short_conv_kernel<T, NIT, 0>, grid, dim3(kCvThreads), 0, st, in, ld_in, P, tail, tail_slot_stride, tail_cols, seqs, row_seq, pairs);
   }
 }
 
@@ -182,8 +227,23 @@ int b200_short_conv(const void* in, int64_t ld_in, const b200_conv_group* groups
   const int per = kCvThreads / 32;
   B200_CHECK_ARG((P.total_heads + per - 1) / per <= 65535, "b200_short_conv: too many heads");
   const dim3 grid((unsigned)rows, (unsigned)((P.total_heads + per - 1) / per));
-  B200_FLOAT_TYPES(dtype, T, B200_CUDA(launch(short_conv_kernel<T>, grid, dim3(kCvThreads), 0, (cudaStream_t)stream, (const T*)in, ld_in, P,
-                                               (const T*)tail, tail_slot_stride, tail_cols, reinterpret_cast<const int4*>(seqs), row_seq)));
+  // pairs of neighbouring channels are read with one access when every head starts on an even channel of even-pitched, aligned rows
+  const size_t esz = dtype == B200_F32 ? 4 : 2;
+  int pairs = (ld_in % 2 == 0) && (tail_cols % 2 == 0) && (tail_slot_stride % 2 == 0) && (reinterpret_cast<uintptr_t>(in) % (2 * esz) == 0) &&
+              (reinterpret_cast<uintptr_t>(tail) % (2 * esz) == 0);
+  int max_dim = 0;
+  for (int i = 0; i < n_groups; ++i) {
+    pairs = pairs && groups[i].dim % 2 == 0 && groups[i].col0 % 2 == 0;
+    max_dim = groups[i].dim > max_dim ? groups[i].dim : max_dim;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int4* sq = reinterpret_cast<const int4*>(seqs);
+  B200_FLOAT_TYPES(dtype, T, {
+    if (max_dim <= 64) B200_CUDA((short_conv_launch<T, 1>(taps, grid, st, (const T*)in, ld_in, P, (const T*)tail, tail_slot_stride, tail_cols, sq, row_seq, pairs)));
+    else if (max_dim <= 128) B200_CUDA((short_conv_launch<T, 2>(taps, grid, st, (const T*)in, ld_in, P, (const T*)tail, tail_slot_stride, tail_cols, sq, row_seq, pairs)));
+    else if (max_dim <= 256) B200_CUDA((short_conv_launch<T, 4>(taps, grid, st, (const T*)in, ld_in, P, (const T*)tail, tail_slot_stride, tail_cols, sq, row_seq, pairs)));
+    else B200_CUDA((short_conv_launch<T, kCvMaxIt>(taps, grid, st, (const T*)in, ld_in, P, (const T*)tail, tail_slot_stride, tail_cols, sq, row_seq, pairs)));
+  });
   return B200_OK;
 }
 

@@ -13,7 +13,7 @@
 //
 //  * window_attn_kernel: 64 query rows x 64 keys per tile (the shape of latent_prefill_kernel), for steps with many rows.
 //  * window_decode_kernel: one CTA per (sequence, head) for single rows: scores of the whole window in shared memory, one
-//    pass for the softmax, then the value sum with the window split over the warps.
+//    pass for the softmax, then the value sum with the window split over thread rows; 16-byte loads where the operands allow.
 #include "common.cuh"
 
 namespace b200 {
@@ -196,13 +196,18 @@ __global__ void __launch_bounds__(kWaThreads) window_attn_kernel(WaArgs A) {
   }
 }
 
-// One row per sequence.  grid (n_head, n_seqs), 128 threads.  Scores for the whole window sit in shared memory.
-constexpr int kWdThreads = 128;
+// One row per sequence.  grid (n_head, n_seqs), 256 threads.  Scores for the whole window sit in shared memory.
+// VEC (every row of q, k, v and the rings starts on a 16-byte boundary and dk, dv are multiples of 8): eight lanes share one
+// key and read it in 8-element pieces, so a warp takes four keys per pass; for the value sum a thread owns eight neighbouring
+// columns and the window is split over the 256 / (dv / 8) thread rows, whose partial sums are added in a fixed order.
+constexpr int kWdThreads = 256, kWdWarps = kWdThreads / 32;
 
-template <typename T>
+__host__ __device__ inline int wd_value_rows(int dv, bool vec) { return vec ? kWdThreads / (dv / 8) : kWdWarps; }
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
   extern __shared__ __align__(16) float wd_smem[];
-  __shared__ float s_red[kWdThreads / 32];
+  __shared__ float s_red[kWdWarps];
   griddep_launch();
   griddep_wait();
   const int h = blockIdx.x, g = h / (A.n_head / A.n_kv_head), G = A.n_kv_head;
@@ -210,29 +215,57 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
   const int row = sq.x, pos = sq.z, slot = sq.w;
   const int dk = A.dk, dv = A.dv;
   const int lo = max(0, pos - A.window + 1), n = pos - lo + 1;     // visible positions lo .. pos
-  float* const qs = wd_smem;            // [dk]
-  float* const sc = qs + dk;            // [n]
-  float* const part = sc + A.window;    // [warps][dv]
+  float* const qs = wd_smem;                        // [dk rounded up to 8]
+  float* const sc = qs + ((dk + 7) & ~7);           // [window rounded up to 4]
+  float* const part = sc + ((A.window + 3) & ~3);   // [value rows][dv]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* const kr = reinterpret_cast<const T*>(A.k_ring);
   const T* const vr = reinterpret_cast<const T*>(A.v_ring);
+  const T* const k_now = reinterpret_cast<const T*>(A.k) + (int64_t)row * A.ldk + (int64_t)g * dk;
+  const T* const v_now = reinterpret_cast<const T*>(A.v) + (int64_t)row * A.ldv + (int64_t)g * dv;
+  auto key_row = [&](int p) { return p == pos ? k_now : kr + ((int64_t)slot * A.ring + p % A.ring) * G * dk + (int64_t)g * dk; };
+  auto value_row = [&](int p) { return p == pos ? v_now : vr + ((int64_t)slot * A.ring + p % A.ring) * G * dv + (int64_t)g * dv; };
   for (int d = tid; d < dk; d += kWdThreads) qs[d] = load_as_float(reinterpret_cast<const T*>(A.q), (int64_t)row * A.ldq + (int64_t)h * dk + d) * A.scale_log2;
   __syncthreads();
-  // scores: one warp per key
   float mx = -INFINITY;
-  for (int j = warp; j < n; j += kWdThreads / 32) {
-    const int p = lo + j;
-    const T* kp = p == pos ? reinterpret_cast<const T*>(A.k) + (int64_t)row * A.ldk + (int64_t)g * dk
-                           : kr + ((int64_t)slot * A.ring + p % A.ring) * G * dk + (int64_t)g * dk;
-    float acc = 0.f;
-    for (int d = lane; d < dk; d += 32) acc = fmaf(qs[d], load_as_float(kp, d), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) sc[j] = acc;
-    mx = fmaxf(mx, acc);
+  if (VEC) {
+    const int sub = tid & 7, grp = tid >> 3;          // 32 groups of eight lanes, one key each per pass
+    for (int jb = 0; jb < n; jb += kWdThreads / 8) {
+      const int j = jb + grp;
+      float acc = 0.f;
+      if (j < n) {
+        const T* kp = key_row(lo + j);
+        for (int c = sub * 8; c < dk; c += 64) {
+          float f[8];
+          load8(kp + c, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc = fmaf(qs[c + e], f[e], acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (j < n) {
+        if (sub == 0) sc[j] = acc;
+        mx = fmaxf(mx, acc);
+      }
+    }
+  } else {
+    for (int j = warp; j < n; j += kWdWarps) {       // one warp per key
+      const T* kp = key_row(lo + j);
+      float acc = 0.f;
+      for (int d = lane; d < dk; d += 32) acc = fmaf(qs[d], load_as_float(kp, d), acc);
+      acc = warp_sum(acc);
+      if (lane == 0) sc[j] = acc;
+      mx = fmaxf(mx, acc);
+    }
   }
+  mx = warp_max(mx);
   if (lane == 0) s_red[warp] = mx;
   __syncthreads();
-  mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+  mx = s_red[0];
+#pragma unroll
+  for (int w = 1; w < kWdWarps; ++w) mx = fmaxf(mx, s_red[w]);
   const float sink_l2 = A.sink ? load_as_float(reinterpret_cast<const T*>(A.sink), h) * kLog2e : -INFINITY;
   mx = fmaxf(mx, sink_l2);
   float sum = 0.f;
@@ -244,22 +277,38 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
   sum = warp_sum(sum);
   __syncthreads();                      // s_red read by everyone above
   if (lane == 0) s_red[warp] = sum;
-  __syncthreads();
-  const float inv = 1.0f / (s_red[0] + s_red[1] + s_red[2] + s_red[3] + exp2f(sink_l2 - mx));
-  // values: every warp sums its share of the window for all columns; the shares are added in a fixed order
-  for (int c = lane; c < dv; c += 32) {
-    float acc = 0.f;
-    for (int j = warp; j < n; j += kWdThreads / 32) {
-      const int p = lo + j;
-      const T* vp = p == pos ? reinterpret_cast<const T*>(A.v) + (int64_t)row * A.ldv + (int64_t)g * dv
-                             : vr + ((int64_t)slot * A.ring + p % A.ring) * G * dv + (int64_t)g * dv;
-      acc = fmaf(sc[j], load_as_float(vp, c), acc);
+  __syncthreads();                      // also: every probability is in shared memory
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWdWarps; ++w) total += s_red[w];
+  const float inv = 1.0f / (total + exp2f(sink_l2 - mx));   // the sink joins the denominator once, unscaled
+  const int vrows = wd_value_rows(dv, VEC);
+  if (VEC) {
+    const int ncg = dv / 8, cg = tid % ncg, rj = tid / ncg;
+    if (rj < vrows) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int j = rj; j < n; j += vrows) {
+        float f[8];
+        load8(value_row(lo + j) + cg * 8, f);
+        const float p = sc[j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(p, f[e], acc[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part[rj * dv + cg * 8 + e] = acc[e];
     }
-    part[warp * dv + c] = acc;
+  } else {
+    for (int c = lane; c < dv; c += 32) {
+      float acc = 0.f;
+      for (int j = warp; j < n; j += kWdWarps) acc = fmaf(sc[j], load_as_float(value_row(lo + j), c), acc);
+      part[warp * dv + c] = acc;
+    }
   }
   __syncthreads();
   for (int c = tid; c < dv; c += kWdThreads) {
-    const float t = (part[c] + part[dv + c]) + (part[2 * dv + c] + part[3 * dv + c]);
+    float t = 0.f;
+    for (int r = 0; r < vrows; ++r) t += part[r * dv + c];
     store_from_float(reinterpret_cast<T*>(A.out), (int64_t)row * A.ldo + (int64_t)h * dv + c, t * inv);
   }
 }
@@ -306,15 +355,21 @@ int b200_window_attn(const b200_window_attn_args* a, b200_stream_t stream) {
   const WaArgs A{a->q, a->k, a->v, a->out, a->ldq, a->ldk, a->ldv, a->ldo, a->k_ring, a->v_ring, a->sink, reinterpret_cast<const int4*>(a->seqs),
                  a->ring, a->n_head, a->n_kv_head, a->dk, a->dv, a->window, a->scale * kLog2e};
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem_d = (size_t)(a->dk + a->window + (kWdThreads / 32) * a->dv) * sizeof(float);
+  const size_t esz = a->dtype == B200_F32 ? 4 : 2;
+  auto aligned = [&](const void* p, int64_t ld) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * esz) % 16 == 0; };
+  const bool vec = a->dk % 8 == 0 && a->dv % 8 == 0 && a->dv <= 8 * kWdThreads && aligned(a->k, a->ldk) && aligned(a->v, a->ldv) &&
+                   aligned(a->k_ring, 8) && aligned(a->v_ring, 8);
+  const size_t smem_d = (size_t)(((a->dk + 7) & ~7) + ((a->window + 3) & ~3) + wd_value_rows(a->dv, vec) * a->dv) * sizeof(float);
   if (a->max_q_len == 1 && !g_wa_force_tiled && smem_d <= 160 * 1024 && a->n_head <= 65535) {
     B200_FLOAT_TYPES(a->dtype, T, {
       static PerDeviceOnce once;
       if (smem_d > 48 * 1024 && once.need()) {
-        B200_CUDA(cudaFuncSetAttribute(window_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(window_decode_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        B200_CUDA(cudaFuncSetAttribute(window_decode_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         once.done();
       }
-      B200_CUDA(launch(window_decode_kernel<T>, dim3((unsigned)a->n_head, (unsigned)a->n_seqs), dim3(kWdThreads), smem_d, st, A));
+      if (vec) B200_CUDA(launch(window_decode_kernel<T, true>, dim3((unsigned)a->n_head, (unsigned)a->n_seqs), dim3(kWdThreads), smem_d, st, A));
+      else B200_CUDA(launch(window_decode_kernel<T, false>, dim3((unsigned)a->n_head, (unsigned)a->n_seqs), dim3(kWdThreads), smem_d, st, A));
     });
     return B200_OK;
   }

@@ -101,6 +101,9 @@ class DecodeGraph:
     def capture(self) -> None:
         state = (self.token.clone(), self.pos.clone())
         rng0 = self.rng.clone()   # the warm-up steps below draw from the sampler state: put it back, they are not part of the sequence
+        # a model whose step UPDATES a state (a recurrence, a convolution tail) instead of writing a cache row must not keep what
+        # the warm-up steps did to it: they run the same position twice
+        keep = None if getattr(self.model, "repeatable_steps", True) else [t.clone() for t in self.model.state_tensors()]
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):  # warm-up outside capture: allocates workspaces, sets kernel attributes
@@ -109,6 +112,9 @@ class DecodeGraph:
                 self._step()
         torch.cuda.current_stream().wait_stream(side)
         self.token.copy_(state[0]); self.pos.copy_(state[1])
+        if keep is not None:
+            for t, saved in zip(self.model.state_tensors(), keep):
+                t.copy_(saved)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._step()

@@ -91,6 +91,8 @@ class LefalixBlock(nn.Module):
 
 
 class Lefalix(SlotServed, nn.Module):
+    repeatable_steps = False   # a step advances recurrent states and convolution tails: repeating it is not idempotent
+
     def __init__(self, config: LefalixConfig) -> None:
         super().__init__()
         self.config = config

@@ -76,6 +76,7 @@ class SlotServed:
     ``set_kv_cache`` / ``clear_kv_cache`` and ``state_tensors()`` (every per-slot buffer, slot first)."""
 
     supports_prefill_graph = False   # a prompt's extent is read on the host
+    repeatable_steps = True          # running a step twice at the same position leaves the same cache (false for recurrent states)
     tp_world_size = 1
 
     @property
