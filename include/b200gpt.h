@@ -525,6 +525,8 @@ typedef struct b200_window_attn_args {
   int n_seqs, max_q_len, ring, n_head, n_kv_head, dk, dv, window;
   float scale;
   int dtype;
+  const int32_t* row_seq;   /* given (with rows): the step's rows also enter the rings, as b200_ring_store does; NULL: rings untouched */
+  int64_t rows;
 } b200_window_attn_args;
 int b200_window_attn(const b200_window_attn_args* args, b200_stream_t stream);
 /* test knob: non-zero keeps single-row steps on the tiled kernel; returns the previous setting */

@@ -116,7 +116,7 @@ class WindowAttnArgs(ctypes.Structure):  # mirrors b200_window_attn_args
     _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p), ("ldq", c_int64), ("ldk", c_int64), ("ldv", c_int64),
                 ("ldo", c_int64), ("k_ring", c_void_p), ("v_ring", c_void_p), ("sink", c_void_p), ("seqs", c_void_p), ("n_seqs", c_int),
                 ("max_q_len", c_int), ("ring", c_int), ("n_head", c_int), ("n_kv_head", c_int), ("dk", c_int), ("dv", c_int), ("window", c_int),
-                ("scale", c_float), ("dtype", c_int)]
+                ("scale", c_float), ("dtype", c_int), ("row_seq", c_void_p), ("rows", c_int64)]
 
 
 ROUTE_SOFTMAX, ROUTE_GROUP_MAX = 1, 2

@@ -7,15 +7,15 @@
 //   with beta = sigmoid(b) and g = exp(-exp(A_log) * softplus(a + dt_bias)) computed here in fp32 from the raw projections.
 //
 // The columns of S never mix: column j evolves from (k, q, g, beta) and v[j] alone.  So the work of one (sequence, head) is
-// split over columns -- a group of LPC lanes owns one column, each lane holding dk / LPC of its numbers in registers -- and
-// over CTAs (column blocks).  Time is walked in order: tiles of tokens are staged in shared memory (keys, queries, decays
+// split over columns -- a group of LPC lanes (16 or 32) owns one column, each lane holding dk / LPC of its numbers in registers
+// -- and over CTAs (column blocks of 8 or 4).  Time is walked in order: tiles of tokens are staged in shared memory (keys, queries, decays
 // already turned into g) while the previous tile is walked; per token every lane group does three short dot products that
 // share one reduction (o = (g S)^T q + (k . q) u needs no second pass over the updated state) and one update.  One kernel serves
 // prompts (many rows per sequence) and decoding (one row: the cost is reading and writing S once).
 //
 // A sequence that starts at position 0 starts from S = 0 whatever its slot holds.  The state is stored in the order the
-// lanes read it: element (key i, column j) of a head at ((i / LPC) * dv + j) * LPC + i % LPC, so that a warp moves 128
-// contiguous bytes per register.
+// kernel's lane groups read whole 32-byte sectors: element (key i, column j) of a head at ((i / L) * dv + j) * L + i % L with
+// L = 4, 8, 16 or 32 by key size (b200_delta_rule_state_floats).
 //
 // b200_gated_rms_heads is the step after the read-out: per head, o / sqrt(mean(o^2) + eps) * weight * gate(z) with
 // gate = silu or sigmoid.
@@ -25,7 +25,7 @@ namespace b200 {
 
 namespace {
 
-constexpr int kDrThreads = 128, kDrKPL = 16;   // keys per lane (registers of state per thread)
+constexpr int kDrThreads = 128, kDrTile = 1024;   // floats of keys (queries, decays) staged per tile
 
 __host__ __device__ inline int delta_lpc(int dk) { return dk <= 64 ? 4 : dk <= 128 ? 8 : dk <= 256 ? 16 : 32; }
 __host__ __device__ inline int delta_key_rows(int dk) { const int l = delta_lpc(dk); return (dk + l - 1) / l; }
@@ -44,10 +44,13 @@ struct DrArgs {
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
-template <typename T, int LPC, bool CHANNEL>
-__global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A) {
-  constexpr int TT = 64 / LPC;                 // tokens per staged tile
-  constexpr int DKP = kDrKPL * LPC;            // padded key size
+// LPC lanes share one column of S, each holding KPL of its numbers (key i = r * LPC + lane); L is the group size of the stored
+// layout, which does not depend on how the kernel spreads a column over lanes.
+template <typename T, int LPC, int KPL, bool CHANNEL>
+__global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A, int L) {
+  constexpr int kDrKPL = KPL;
+  constexpr int DKP = KPL * LPC;               // padded key size
+  constexpr int TT = kDrTile / DKP;            // tokens per staged tile
   constexpr int COLS = kDrThreads / LPC;       // columns per CTA
   constexpr int NIT = TT * DKP / kDrThreads;   // key elements of a tile per thread (8)
   constexpr int NV = (TT * COLS + kDrThreads - 1) / kDrThreads;   // value elements of a tile per thread
@@ -66,12 +69,19 @@ __global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A) {
   const int col = (int)blockIdx.x * COLS + cl;
   const bool col_ok = col < A.dv;
   const int dk = A.dk, dv = A.dv;
-  const int krows = (dk + LPC - 1) / LPC;
-  float* const st = A.state + (int64_t)slot * A.state_slot_stride + (int64_t)h * krows * LPC * dv;
+  const int krows = (dk + L - 1) / L;           // rows of L keys in the stored layout
+  float* const st = A.state + (int64_t)slot * A.state_slot_stride + (int64_t)h * krows * L * dv;
+  auto where = [&](int r) -> int64_t {          // key r * LPC + sub of this lane's column; -1 past the padded key size
+    const int i = r * LPC + sub;
+    return i < krows * L ? ((int64_t)(i / L) * dv + col) * L + i % L : -1;
+  };
 
   float S[kDrKPL];
 #pragma unroll
-  for (int r = 0; r < kDrKPL; ++r) S[r] = (pos0 > 0 && col_ok && r < krows) ? st[((int64_t)r * dv + col) * LPC + sub] : 0.f;
+  for (int r = 0; r < kDrKPL; ++r) {
+    const int64_t w = where(r);
+    S[r] = (pos0 > 0 && col_ok && w >= 0) ? st[w] : 0.f;
+  }
 
   const float neg_a = -expf(load_as_float(reinterpret_cast<const T*>(A.a_log), h));
   const T* const bias = reinterpret_cast<const T*>(A.dt_bias);
@@ -182,27 +192,24 @@ __global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A) {
   }
   if (col_ok) {
 #pragma unroll
-    for (int r = 0; r < kDrKPL; ++r)
-      if (r < krows) st[((int64_t)r * dv + col) * LPC + sub] = S[r];
+    for (int r = 0; r < kDrKPL; ++r) {
+      const int64_t w = where(r);
+      if (w >= 0) st[w] = S[r];
+    }
   }
 }
 
-template <typename T, int LPC>
+template <typename T, int LPC, int KPL>
 cudaError_t delta_launch(const DrArgs& A, bool channel, int n_seqs, cudaStream_t st) {
-  constexpr int TT = 64 / LPC, DKP = kDrKPL * LPC, COLS = kDrThreads / LPC;
+  constexpr int DKP = KPL * LPC, TT = kDrTile / DKP, COLS = kDrThreads / LPC;
   const dim3 grid((unsigned)((A.dv + COLS - 1) / COLS), (unsigned)A.heads, (unsigned)n_seqs);
+  const int L = delta_lpc(A.dk);
   if (channel) {
     const size_t smem = (size_t)(3 * TT * DKP + TT * COLS + TT) * sizeof(float);
-    static PerDeviceOnce once;
-    if (smem > 48 * 1024 && once.need()) {
-      cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<T, LPC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return e;
-      once.done();
-    }
-    return launch(delta_rule_kernel<T, LPC, true>, grid, dim3(kDrThreads), smem, st, A);
+    return launch(delta_rule_kernel<T, LPC, KPL, true>, grid, dim3(kDrThreads), smem, st, A, L);
   }
   const size_t smem = (size_t)(2 * TT * DKP + TT + TT * COLS + TT) * sizeof(float);
-  return launch(delta_rule_kernel<T, LPC, false>, grid, dim3(kDrThreads), smem, st, A);
+  return launch(delta_rule_kernel<T, LPC, KPL, false>, grid, dim3(kDrThreads), smem, st, A, L);
 }
 
 // out[row, h, :] = T( o / sqrt(mean(o^2) + eps) * weight * gate(z[row, h, :]) ); one warp per (row, head)
@@ -242,18 +249,19 @@ int b200_delta_rule(const b200_delta_rule_args* a, b200_stream_t stream) {
                  "b200_delta_rule: null pointer");
   B200_CHECK_ARG(a->n_seqs > 0 && a->n_seqs <= 65535 && a->heads > 0 && a->heads <= 65535 && a->kv_heads > 0 && a->heads % a->kv_heads == 0,
                  "b200_delta_rule: bad head counts");
-  B200_CHECK_ARG(a->dk > 0 && a->dk <= kDrKPL * 32 && a->dv > 0, "b200_delta_rule: key size must be 1 .. %d", kDrKPL * 32);
+  B200_CHECK_ARG(a->dk > 0 && a->dk <= 512 && a->dv > 0, "b200_delta_rule: key size must be 1 .. 512");
   B200_CHECK_ARG((reinterpret_cast<uintptr_t>(a->seqs) & 15) == 0, "b200_delta_rule: seqs must be 16-byte aligned");
   const DrArgs A{a->q, a->k, a->v, a->ldq, a->ldk, a->ldv, a->beta_in, a->ld_beta, a->decay_in, a->ld_decay, a->a_log, a->dt_bias,
                  a->state, a->state_slot_stride, a->out, a->ldo, reinterpret_cast<const int4*>(a->seqs), a->heads, a->kv_heads, a->dk, a->dv};
   const bool ch = a->channel_decay != 0;
   cudaStream_t st = (cudaStream_t)stream;
-  const int lpc = delta_lpc(a->dk);
+  // a column is spread over as many lanes as its key size fills with a few numbers each: short dependent chains per token and
+  // four times the warps of a 16-keys-per-lane split, which is what a token-serial walk over one or a few sequences needs
   B200_FLOAT_TYPES(a->dtype, T, {
-    if (lpc == 4) B200_CUDA((delta_launch<T, 4>(A, ch, a->n_seqs, st)));
-    else if (lpc == 8) B200_CUDA((delta_launch<T, 8>(A, ch, a->n_seqs, st)));
-    else if (lpc == 16) B200_CUDA((delta_launch<T, 16>(A, ch, a->n_seqs, st)));
-    else B200_CUDA((delta_launch<T, 32>(A, ch, a->n_seqs, st)));
+    if (a->dk <= 64) B200_CUDA((delta_launch<T, 16, 4>(A, ch, a->n_seqs, st)));
+    else if (a->dk <= 128) B200_CUDA((delta_launch<T, 32, 4>(A, ch, a->n_seqs, st)));
+    else if (a->dk <= 256) B200_CUDA((delta_launch<T, 32, 8>(A, ch, a->n_seqs, st)));
+    else B200_CUDA((delta_launch<T, 32, 16>(A, ch, a->n_seqs, st)));
   });
   return B200_OK;
 }

@@ -8,8 +8,9 @@
 //
 // Only the last `ring` >= window positions of a sequence are kept: position p lives in row p % ring of the sequence's slot.
 // A step's own keys and values are read from the step's packed rows (k, v), older ones from the ring, so one kernel serves
-// a whole prompt, a later portion of one and single decoded tokens; b200_ring_store puts the step's last rows into the
-// ring AFTERWARDS (a long step would otherwise overwrite ring rows that its first queries still need).
+// a whole prompt, a later portion of one and single decoded tokens; the step's last rows enter the ring AFTERWARDS (a long
+// step would otherwise overwrite ring rows that its first queries still need): b200_ring_store after the tiled kernel, the
+// single-row kernel itself for its one row.
 //
 //  * window_attn_kernel: 64 query rows x 64 keys per tile (the shape of latent_prefill_kernel), for steps with many rows.
 //  * window_decode_kernel: one CTA per (sequence, head) for single rows: scores of the whole window in shared memory, one
@@ -37,6 +38,7 @@ struct WaArgs {
   const int4* seqs;
   int ring, n_head, n_kv_head, dk, dv, window;
   float scale_log2;
+  int store_ring;
 };
 
 template <typename T>
@@ -230,24 +232,64 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
   float mx = -INFINITY;
   if (VEC) {
     const int sub = tid & 7, grp = tid >> 3;          // 32 groups of eight lanes, one key each per pass
-    for (int jb = 0; jb < n; jb += kWdThreads / 8) {
-      const int j = jb + grp;
-      float acc = 0.f;
-      if (j < n) {
-        const T* kp = key_row(lo + j);
-        for (int c = sub * 8; c < dk; c += 64) {
-          float f[8];
-          load8(kp + c, f);
+    constexpr int KG = kWdThreads / 8, U = 4;         // four passes' loads are issued before any of them is used
+    for (int jb = 0; jb < n; jb += KG * U) {
+      float acc[U];
+      if (dk <= 128) {
+        float f[U][2][8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc = fmaf(qs[c + e], f[e], acc);
+        for (int u = 0; u < U; ++u) {
+          const int j = jb + u * KG + grp;
+          const T* kp = key_row(lo + min(j, n - 1));
+#pragma unroll
+          for (int pc = 0; pc < 2; ++pc) {
+            const int c = sub * 8 + pc * 64;
+            if (j < n && c < dk) load8(kp + c, f[u][pc]);
+            else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[u][pc][e] = 0.f;
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          acc[u] = 0.f;
+#pragma unroll
+          for (int pc = 0; pc < 2; ++pc) {
+            const int c = sub * 8 + pc * 64;
+            if (c < dk) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[u] = fmaf(qs[c + e], f[u][pc][e], acc[u]);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = jb + u * KG + grp;
+          acc[u] = 0.f;
+          if (j < n) {
+            const T* kp = key_row(lo + j);
+            for (int c = sub * 8; c < dk; c += 64) {
+              float f[8];
+              load8(kp + c, f);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[u] = fmaf(qs[c + e], f[e], acc[u]);
+            }
+          }
         }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (j < n) {
-        if (sub == 0) sc[j] = acc;
-        mx = fmaxf(mx, acc);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int j = jb + u * KG + grp;
+        float a = acc[u];
+        a += __shfl_xor_sync(0xffffffffu, a, 4);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        if (j < n) {
+          if (sub == 0) sc[j] = a;
+          mx = fmaxf(mx, a);
+        }
       }
     }
   } else {
@@ -311,6 +353,14 @@ __global__ void __launch_bounds__(kWdThreads) window_decode_kernel(WaArgs A) {
     for (int r = 0; r < vrows; ++r) t += part[r * dv + c];
     store_from_float(reinterpret_cast<T*>(A.out), (int64_t)row * A.ldo + (int64_t)h * dv + c, t * inv);
   }
+  // The row's own key and value enter the ring here: they replace position pos - ring, which no row of this step can see
+  // (ring >= window), and every CTA reads the current position from the step's rows, never from the ring.
+  if (A.store_ring && h % (A.n_head / G) == 0) {
+    T* kd = const_cast<T*>(kr) + ((int64_t)slot * A.ring + pos % A.ring) * G * dk + (int64_t)g * dk;
+    T* vd = const_cast<T*>(vr) + ((int64_t)slot * A.ring + pos % A.ring) * G * dv + (int64_t)g * dv;
+    for (int d = tid; d < dk; d += kWdThreads) kd[d] = k_now[d];
+    for (int c = tid; c < dv; c += kWdThreads) vd[c] = v_now[c];
+  }
 }
 
 // ring[slot][p % ring] <- row, for the rows whose position p is among the sequence's last `ring`
@@ -353,7 +403,7 @@ int b200_window_attn(const b200_window_attn_args* a, b200_stream_t stream) {
   B200_CHECK_ARG(a->window > 0 && a->ring >= a->window && a->k_ring && a->v_ring, "b200_window_attn: the ring must hold at least one window");
   B200_CHECK_ARG((reinterpret_cast<uintptr_t>(a->seqs) & 15) == 0, "b200_window_attn: seqs must be 16-byte aligned");
   const WaArgs A{a->q, a->k, a->v, a->out, a->ldq, a->ldk, a->ldv, a->ldo, a->k_ring, a->v_ring, a->sink, reinterpret_cast<const int4*>(a->seqs),
-                 a->ring, a->n_head, a->n_kv_head, a->dk, a->dv, a->window, a->scale * kLog2e};
+                 a->ring, a->n_head, a->n_kv_head, a->dk, a->dv, a->window, a->scale * kLog2e, a->row_seq != nullptr};
   cudaStream_t st = (cudaStream_t)stream;
   const size_t esz = a->dtype == B200_F32 ? 4 : 2;
   auto aligned = [&](const void* p, int64_t ld) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * esz) % 16 == 0; };
@@ -386,6 +436,9 @@ int b200_window_attn(const b200_window_attn_args* a, b200_stream_t stream) {
     B200_CHECK_ARG(smem <= 200 * 1024, "b200_window_attn: head size too large for the tile");
     B200_CUDA(launch(window_attn_kernel<T>, grid, dim3(kWaThreads), smem, st, A));
   });
+  if (a->row_seq)
+    return b200_ring_store(a->k, a->ldk, a->v, a->ldv, const_cast<void*>(a->k_ring), const_cast<void*>(a->v_ring), a->ring, a->n_kv_head * a->dk,
+                           a->n_kv_head * a->dv, a->seqs, a->row_seq, a->rows, a->dtype, stream);
   return B200_OK;
 }
 

@@ -926,19 +926,16 @@ def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch
         C.check(lib.b200_attn_prefill_window(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), seqs.data_ptr(),
                                              seqs.shape[0], max_q_len, out.data_ptr(), out.stride(0), n_head, n_kv_head, dk, float(scale), window,
                                              C.ptr(sink), st), "attn_prefill_window")
-    else:
-        _window_attn_any(lib, st, q, k, v, out, k_ring, v_ring, sink, seqs, max_q_len, ring, n_head, n_kv_head, dk, dv, window, scale)
-    C.check(lib.b200_ring_store(k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_ring.data_ptr(), v_ring.data_ptr(), ring, n_kv_head * dk,
-                                n_kv_head * dv, seqs.data_ptr(), row_seq.data_ptr(), q.shape[0], _code(q), st), "ring_store")
-    return out
-
-
-def _window_attn_any(lib, st, q, k, v, out, k_ring, v_ring, sink, seqs, max_q_len, ring, n_head, n_kv_head, dk, dv, window, scale) -> None:
-    args = C.WindowAttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
+        C.check(lib.b200_ring_store(k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), k_ring.data_ptr(), v_ring.data_ptr(), ring, n_kv_head * dk,
+                                    n_kv_head * dv, seqs.data_ptr(), row_seq.data_ptr(), q.shape[0], _code(q), st), "ring_store")
+        return out
+    # the any-size kernels store the step's rows into the rings themselves (single rows: inside the attention kernel)
+    args = C.WindowAttnArgs(row_seq=row_seq.data_ptr(), rows=q.shape[0], q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
                             ldo=out.stride(0), k_ring=k_ring.data_ptr(), v_ring=v_ring.data_ptr(), sink=C.ptr(sink), seqs=seqs.data_ptr(),
                             n_seqs=seqs.shape[0], max_q_len=max_q_len, ring=ring, n_head=n_head, n_kv_head=n_kv_head, dk=dk, dv=dv, window=window,
                             scale=float(scale), dtype=_code(q))
     C.check(lib.b200_window_attn(ctypes.byref(args), st), "window_attn")
+    return out
 
 
 def window_attn_tune(force_tiled_kernel: bool = False) -> bool:
