@@ -729,7 +729,7 @@ def run_lefalix_compare(args) -> None:
                 be, de = torch.randn(T, Hd, device=dev, dtype=bf), torch.randn(T, Hd * hs if ch else Hd, device=dev, dtype=bf)
                 al, db = torch.zeros(Hd, device=dev, dtype=bf), torch.zeros(Hd * hs if ch else Hd, device=dev, dtype=bf)
                 st1 = torch.zeros(1, floats, device=dev)
-                ms = _timed(lambda: K.delta_rule(qf, kf, vf, be, de, al, db, st1, batch.seq_state, Hd, Gd, hs, hs, ch), iters, flush)
+                ms = _timed(lambda: K.delta_rule(qf, kf, vf, be, de, al, db, st1, batch.seq_state, Hd, Gd, hs, hs, ch, max_rows=T), iters, flush)
                 kern[f"delta_rule_prompt_{label}_decay"] = {"ms": ms, "us_per_token": ms * 1e3 / T, "fp32_tflops": 6.0 * T * Hd * hs * hs / (ms * 1e-3) / 1e12}
                 st8 = torch.zeros(B, floats, device=dev)
                 ms = _timed(lambda: K.delta_rule(qf[:B], kf[:B], vf[:B], be[:B], de[:B], al, db, st8, bd.seq_state, Hd, Gd, hs, hs, ch), iters, flush)

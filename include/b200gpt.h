@@ -506,6 +506,7 @@ typedef struct b200_delta_rule_args {
   float* out; int64_t ldo;
   const int32_t* seqs; int n_seqs;
   int heads, kv_heads, dk, dv, channel_decay, dtype;
+  int max_rows;   /* the longest sequence's rows in this step (a hint for the launch shape; 0: unknown, treated as 1) */
 } b200_delta_rule_args;
 int64_t b200_delta_rule_state_floats(int dk, int dv);
 int b200_delta_rule(const b200_delta_rule_args* args, b200_stream_t stream);

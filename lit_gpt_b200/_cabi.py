@@ -109,7 +109,7 @@ class DeltaRuleArgs(ctypes.Structure):  # mirrors b200_delta_rule_args
                 ("beta_in", c_void_p), ("ld_beta", c_int64), ("decay_in", c_void_p), ("ld_decay", c_int64), ("a_log", c_void_p),
                 ("dt_bias", c_void_p), ("state", c_void_p), ("state_slot_stride", c_int64), ("out", c_void_p), ("ldo", c_int64),
                 ("seqs", c_void_p), ("n_seqs", c_int), ("heads", c_int), ("kv_heads", c_int), ("dk", c_int), ("dv", c_int),
-                ("channel_decay", c_int), ("dtype", c_int)]
+                ("channel_decay", c_int), ("dtype", c_int), ("max_rows", c_int)]
 
 
 class WindowAttnArgs(ctypes.Structure):  # mirrors b200_window_attn_args

@@ -7,8 +7,8 @@
 //   with beta = sigmoid(b) and g = exp(-exp(A_log) * softplus(a + dt_bias)) computed here in fp32 from the raw projections.
 //
 // The columns of S never mix: column j evolves from (k, q, g, beta) and v[j] alone.  So the work of one (sequence, head) is
-// split over columns -- a group of LPC lanes (16 or 32) owns one column, each lane holding dk / LPC of its numbers in registers
-// -- and over CTAs (column blocks of 8 or 4).  Time is walked in order: tiles of tokens are staged in shared memory (keys, queries, decays
+// split over columns -- a group of LPC lanes owns one column, each lane holding dk / LPC of its numbers in registers -- and
+// over CTAs (column blocks); the host picks LPC (see b200_delta_rule).  Time is walked in order: tiles of tokens are staged in shared memory (keys, queries, decays
 // already turned into g) while the previous tile is walked; per token every lane group does three short dot products that
 // share one reduction (o = (g S)^T q + (k . q) u needs no second pass over the updated state) and one update.  One kernel serves
 // prompts (many rows per sequence) and decoding (one row: the cost is reading and writing S once).
@@ -255,13 +255,23 @@ int b200_delta_rule(const b200_delta_rule_args* a, b200_stream_t stream) {
                  a->state, a->state_slot_stride, a->out, a->ldo, reinterpret_cast<const int4*>(a->seqs), a->heads, a->kv_heads, a->dk, a->dv};
   const bool ch = a->channel_decay != 0;
   cudaStream_t st = (cudaStream_t)stream;
-  // a column is spread over as many lanes as its key size fills with a few numbers each: short dependent chains per token and
-  // four times the warps of a 16-keys-per-lane split, which is what a token-serial walk over one or a few sequences needs
+  // Two ways to spread a column over lanes.  Few lanes with 16 numbers each: three reduction rounds per token and whole
+  // 128-byte lines of state per warp -- best for single tokens and for the per-head decay.  A prompt with per-channel decays
+  // carries a third staged array and the softplus / exponential of every decay: there a column on 16 or 32 lanes with 4 or 8
+  // numbers each (four times the warps) measured faster (0.66 against 0.85 us per token at 8 heads of 128 x 128).
+  const bool wide = ch && a->max_rows > 1 && a->dk > 32 && a->dk <= 256;
   B200_FLOAT_TYPES(a->dtype, T, {
-    if (a->dk <= 64) B200_CUDA((delta_launch<T, 16, 4>(A, ch, a->n_seqs, st)));
-    else if (a->dk <= 128) B200_CUDA((delta_launch<T, 32, 4>(A, ch, a->n_seqs, st)));
-    else if (a->dk <= 256) B200_CUDA((delta_launch<T, 32, 8>(A, ch, a->n_seqs, st)));
-    else B200_CUDA((delta_launch<T, 32, 16>(A, ch, a->n_seqs, st)));
+    if (wide) {
+      if (a->dk <= 64) B200_CUDA((delta_launch<T, 16, 4>(A, ch, a->n_seqs, st)));
+      else if (a->dk <= 128) B200_CUDA((delta_launch<T, 32, 4>(A, ch, a->n_seqs, st)));
+      else B200_CUDA((delta_launch<T, 32, 8>(A, ch, a->n_seqs, st)));
+    } else {
+      const int lpc = delta_lpc(a->dk);
+      if (lpc == 4) B200_CUDA((delta_launch<T, 4, 16>(A, ch, a->n_seqs, st)));
+      else if (lpc == 8) B200_CUDA((delta_launch<T, 8, 16>(A, ch, a->n_seqs, st)));
+      else if (lpc == 16) B200_CUDA((delta_launch<T, 16, 16>(A, ch, a->n_seqs, st)));
+      else B200_CUDA((delta_launch<T, 32, 16>(A, ch, a->n_seqs, st)));
+    }
   });
   return B200_OK;
 }

@@ -87,6 +87,7 @@ class GatedDeltaRule(nn.Module):
         else:
             decay_in = proj[:, self.off_decay : self.off_beta]
             gate_in = proj[:, self.off_gate : self.off_decay]
-        o = K.delta_rule(q, k, v, beta_in, decay_in, self.a_log, self.dt_bias, state.matrices, batch.seq_state, H, G, dk, dv, s.channel)
+        o = K.delta_rule(q, k, v, beta_in, decay_in, self.a_log, self.dt_bias, state.matrices, batch.seq_state, H, G, dk, dv, s.channel,
+                         max_rows=batch.max_q_len)
         y = K.gated_rms_heads(o, gate_in, self.norm, H, dv, K.GATE_SIGMOID if s.channel else K.GATE_SILU, self.eps)
         return F.linear(y, self.w_o)

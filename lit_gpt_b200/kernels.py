@@ -866,9 +866,10 @@ def delta_rule_state_floats(dk: int, dv: int) -> int:
 
 def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_in: torch.Tensor, decay_in: torch.Tensor, a_log: torch.Tensor,
                dt_bias: torch.Tensor, state: torch.Tensor, seqs: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int,
-               channel_decay: bool) -> torch.Tensor:
+               channel_decay: bool, max_rows: int = 0) -> torch.Tensor:
     """Gated delta rule over the step's rows; state (slots, floats) fp32 is read (unless the sequence starts at 0) and written.
-    q, k (n, kv_heads * dk), v (n, heads * dv) fp32; beta_in (n, heads), decay_in (n, heads [* dk]) raw projections.  -> fp32 (n, heads * dv)"""
+    q, k (n, kv_heads * dk), v (n, heads * dv) fp32; beta_in (n, heads), decay_in (n, heads [* dk]) raw projections; max_rows: the
+    longest sequence's rows in this step (picks the launch shape).  -> fp32 (n, heads * dv)"""
     C.require_cuda(q, k, v, beta_in, decay_in, a_log, dt_bias, state, seqs)
     if not (q.dtype == k.dtype == v.dtype == state.dtype == torch.float32) or seqs.dtype != torch.int32 or not seqs.is_contiguous():
         raise C.B200Error("delta_rule: q, k, v and the state are fp32, seqs int32")
@@ -884,7 +885,7 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_in: torch
                            beta_in=beta_in.data_ptr(), ld_beta=beta_in.stride(0), decay_in=decay_in.data_ptr(), ld_decay=decay_in.stride(0),
                            a_log=a_log.data_ptr(), dt_bias=dt_bias.data_ptr(), state=state.data_ptr(), state_slot_stride=state.stride(0),
                            out=out.data_ptr(), ldo=out.stride(0), seqs=seqs.data_ptr(), n_seqs=seqs.shape[0], heads=heads, kv_heads=kv_heads,
-                           dk=dk, dv=dv, channel_decay=int(channel_decay), dtype=_code(beta_in))
+                           dk=dk, dv=dv, channel_decay=int(channel_decay), dtype=_code(beta_in), max_rows=int(max_rows))
     C.check(C.load_core().b200_delta_rule(ctypes.byref(args), C.stream_ptr(q.device)), "delta_rule")
     return out
 

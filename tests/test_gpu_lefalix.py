@@ -344,11 +344,12 @@ def test_sink_takes_probability_once_and_unscaled():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("channel", [False, True])
-@pytest.mark.parametrize("cuts", [[41], [1] * 41, [2, 2, 1, 20, 2, 3, 9, 2], [40, 1]])
-def test_delta_rule_alone(dtype, channel, cuts):
+@pytest.mark.parametrize("cuts,dim", [([41], 12), ([1] * 41, 12), ([2, 2, 1, 20, 2, 3, 9, 2], 12), ([40, 1], 12), ([30, 1, 10], 40), ([3, 37, 1], 72)])
+def test_delta_rule_alone(dtype, channel, cuts, dim):
     """Grouped heads, convolution tail with its activation, unit vectors, decay per head or per channel, write-then-read order,
-    gated norm -- with the state carried over every cut."""
-    m = delta(4, 2, 12, 10, 4)
+    gated norm -- with the state carried over every cut (prompts and single tokens spread a state column over different numbers
+    of lanes for the larger key sizes: both read the same stored state)."""
+    m = delta(4, 2, dim, 10, 4)
     layer = channel_layer(m, None) if channel else parallel_layer(window(1, 1, 4, 4, 1, size=2, rot_dims=4), m, None)
     cfg, w, model = _one_layer(layer, 24, dtype, seed=13)
     g = torch.Generator().manual_seed(15)
@@ -386,7 +387,7 @@ def test_delta_rule_remembers_a_far_write():
         batch, _ = state_batch([(1, at, c)], torch.device("cuda"))
         s = slice(at, at + c)
         outs.append(k.delta_rule(q[s].cuda(), kk[s].cuda(), v[s].cuda(), beta_in[s].cuda(), decay_in[s].cuda(), a_log.cuda(), dt_bias.cuda(), state,
-                                 batch.seq_state, H, 1, dk, dv, False).cpu())
+                                 batch.seq_state, H, 1, dk, dv, False, max_rows=c).cpu())
     last = outs[-1][0]
     assert torch.allclose(last[:dv], v[0, :dv], rtol=1e-5) and float(last[dv:].abs().max()) < 1e-6
 
