@@ -259,7 +259,9 @@ int b200_delta_rule(const b200_delta_rule_args* a, b200_stream_t stream) {
   // 128-byte lines of state per warp -- best for single tokens and for the per-head decay.  A prompt with per-channel decays
   // carries a third staged array and the softplus / exponential of every decay: there a column on 16 or 32 lanes with 4 or 8
   // numbers each (four times the warps) measured faster (0.66 against 0.85 us per token at 8 heads of 128 x 128).
-  const bool wide = ch && a->max_rows > 1 && a->dk > 32 && a->dk <= 256;
+  // (that is with 64 to 128 CTAs of the narrow split; once those alone fill the GPU, more warps only add reduction rounds)
+  const int64_t narrow_ctas = (int64_t)((a->dv + kDrThreads / delta_lpc(a->dk) - 1) / (kDrThreads / delta_lpc(a->dk))) * a->heads * a->n_seqs;
+  const bool wide = ch && a->max_rows > 1 && a->dk > 32 && a->dk <= 256 && narrow_ctas < (int64_t)sm_count() * 3 / 2;
   B200_FLOAT_TYPES(a->dtype, T, {
     if (wide) {
       if (a->dk <= 64) B200_CUDA((delta_launch<T, 16, 4>(A, ch, a->n_seqs, st)));

@@ -168,7 +168,7 @@ struct SandwichArgs {
 
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads) sandwich_residual_kernel(SandwichArgs A) {
-  extern __shared__ float sw_row[];   // [d]
+  extern __shared__ __align__(16) float sw_row[];   // [d]
   __shared__ float s_part[kRowThreads / 32];
   griddep_launch();
   griddep_wait();
@@ -176,44 +176,113 @@ __global__ void __launch_bounds__(kRowThreads) sandwich_residual_kernel(Sandwich
   const int d = A.d;
   const T* y0 = reinterpret_cast<const T*>(A.y0) + row * d;
   const T* y1 = A.y1 ? reinterpret_cast<const T*>(A.y1) + row * d : nullptr;
+  const T* w0 = reinterpret_cast<const T*>(A.w0);
+  const T* w1 = reinterpret_cast<const T*>(A.w1);
+  const T* pw = reinterpret_cast<const T*>(A.post_w);
+  const T* nw = reinterpret_cast<const T*>(A.pre_w);
   float* xr = A.x + row * d;
+  const float* ex = A.extra ? A.extra + row * d : nullptr;
+  T* ar = nw ? reinterpret_cast<T*>(A.act) + row * d : nullptr;
+  // eight elements per access when every row and weight starts on a 16-byte boundary (d a multiple of 8, aligned bases)
+  const bool vec = vec8_ok(d, A.y0, A.y1, A.w0, A.w1) && vec8_ok(d, A.post_w, A.pre_w, A.x, A.act) && vec8_ok(d, A.extra);
   float s0 = 0.f, s1 = 0.f;
-  for (int i = threadIdx.x; i < d; i += kRowThreads) {
-    const float a = load_as_float(y0, i);
-    s0 = fmaf(a, a, s0);
-    if (y1) { const float b = load_as_float(y1, i); s1 = fmaf(b, b, s1); }
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < d; i += kRowThreads * 8) {
+      float a[8];
+      load8(y0 + i, a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s0 = fmaf(a[j], a[j], s0);
+      if (y1) {
+        float b[8];
+        load8(y1 + i, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s1 = fmaf(b[j], b[j], s1);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += kRowThreads) {
+      const float a = load_as_float(y0, i);
+      s0 = fmaf(a, a, s0);
+      if (y1) { const float b = load_as_float(y1, i); s1 = fmaf(b, b, s1); }
+    }
   }
   float ss = 0.f;
   if (y1) {
     const float r0 = 1.0f / sqrtf(cta_sum(s0, s_part) / (float)d + A.eps);
     const float r1 = 1.0f / sqrtf(cta_sum(s1, s_part) / (float)d + A.eps);
-    const T* w0 = reinterpret_cast<const T*>(A.w0);
-    const T* w1 = reinterpret_cast<const T*>(A.w1);
-    for (int i = threadIdx.x; i < d; i += kRowThreads) {
-      const float v = 0.5f * (load_as_float(y0, i) * r0 * load_as_float(w0, i) + load_as_float(y1, i) * r1 * load_as_float(w1, i));
-      sw_row[i] = v;
-      ss = fmaf(v, v, ss);
+    if (vec) {
+      for (int i = threadIdx.x * 8; i < d; i += kRowThreads * 8) {
+        float a[8], b[8], ga[8], gb[8];
+        load8(y0 + i, a); load8(y1 + i, b); load8(w0 + i, ga); load8(w1 + i, gb);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = 0.5f * (a[j] * r0 * ga[j] + b[j] * r1 * gb[j]);
+          sw_row[i + j] = v;
+          ss = fmaf(v, v, ss);
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < d; i += kRowThreads) {
+        const float v = 0.5f * (load_as_float(y0, i) * r0 * load_as_float(w0, i) + load_as_float(y1, i) * r1 * load_as_float(w1, i));
+        sw_row[i] = v;
+        ss = fmaf(v, v, ss);
+      }
     }
   } else {
-    for (int i = threadIdx.x; i < d; i += kRowThreads) sw_row[i] = load_as_float(y0, i);
+    if (vec) {
+      for (int i = threadIdx.x * 8; i < d; i += kRowThreads * 8) {
+        float a[8];
+        load8(y0 + i, a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sw_row[i + j] = a[j];
+      }
+    } else {
+      for (int i = threadIdx.x; i < d; i += kRowThreads) sw_row[i] = load_as_float(y0, i);
+    }
     ss = s0;
   }
   float rp = 1.0f;
-  const T* pw = reinterpret_cast<const T*>(A.post_w);
   if (pw) rp = 1.0f / sqrtf(cta_sum(ss, s_part) / (float)d + A.eps);
   float sx = 0.f;
-  for (int i = threadIdx.x; i < d; i += kRowThreads) {   // each thread touches only the elements it wrote: no barrier needed
-    float v = xr[i] + (pw ? sw_row[i] * rp * load_as_float(pw, i) : sw_row[i]);
-    if (A.extra) v += A.extra[row * d + i];
-    xr[i] = v;
-    sw_row[i] = v;
-    sx = fmaf(v, v, sx);
+  // each thread touches only the elements it wrote: no barrier needed between the passes over sw_row
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < d; i += kRowThreads * 8) {
+      float xv[8], g[8], e[8];
+      load8(xr + i, xv);
+      if (pw) load8(pw + i, g);
+      if (ex) load8(ex + i, e);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v = xv[j] + (pw ? sw_row[i + j] * rp * g[j] : sw_row[i + j]);
+        if (ex) v += e[j];
+        xv[j] = v;
+        sw_row[i + j] = v;
+        sx = fmaf(v, v, sx);
+      }
+      store8(xr + i, xv);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += kRowThreads) {
+      float v = xr[i] + (pw ? sw_row[i] * rp * load_as_float(pw, i) : sw_row[i]);
+      if (ex) v += ex[i];
+      xr[i] = v;
+      sw_row[i] = v;
+      sx = fmaf(v, v, sx);
+    }
   }
-  if (!A.pre_w) return;
-  const T* nw = reinterpret_cast<const T*>(A.pre_w);
-  T* ar = reinterpret_cast<T*>(A.act) + row * d;
+  if (!nw) return;
   const float rn = 1.0f / sqrtf(cta_sum(sx, s_part) / (float)d + A.eps);
-  for (int i = threadIdx.x; i < d; i += kRowThreads) store_from_float(ar, i, sw_row[i] * rn * load_as_float(nw, i));
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < d; i += kRowThreads * 8) {
+      float g[8], o[8];
+      load8(nw + i, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = sw_row[i + j] * rn * g[j];
+      store8(ar + i, o);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += kRowThreads) store_from_float(ar, i, sw_row[i] * rn * load_as_float(nw, i));
+  }
 }
 
 // elementwise activations: kind 0 exact gelu (erf), 1 tanh gelu, 2 silu, 3 relu^2
