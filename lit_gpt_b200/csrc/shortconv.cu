@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(kCvThreads) short_conv_kernel(const T* __restr
   const T* tl = tail + (int64_t)sq.w * tail_slot_stride;
   const T* wt = reinterpret_cast<const T*>(G.w);
   const int c_head = G.col0 + hh * G.dim;     // first channel of this head among the convolved columns
-  const bool pair = pairs != 0;
+  const bool pair = (pairs & 1) != 0;
+  const bool wvec = TAPS == 4 && (pairs & 2) != 0;   // the eight taps of two neighbouring channels in one 16-byte (fp32: 32-byte) access
 
   float val[NIT][2];
   float ss = 0.f;
@@ -97,6 +98,8 @@ __global__ void __launch_bounds__(kCvThreads) short_conv_kernel(const T* __restr
       const bool second = d + 1 < G.dim;
       const int c = c_head + d;
       const T* wc = wt + (int64_t)(hh * G.dim + d) * taps;
+      float wf[8];
+      if (wvec) load8(wc, wf);
 #pragma unroll
       for (int j = 0; j < (TAPS ? TAPS : kCvMaxTaps + 1); ++j) {
         if (!TAPS && j >= taps) break;
@@ -106,8 +109,13 @@ __global__ void __launch_bounds__(kCvThreads) short_conv_kernel(const T* __restr
           if (back <= r) load_pair(in, (row - back) * ld_in + c, pair, second, u0, u1);
           else load_pair(tl, (int64_t)(taps - 1 - (back - r)) * tail_cols + c, pair, second, u0, u1);   // tail row taps-1-k: the k-th row before the step
         }
-        acc0 = fmaf(load_as_float(wc, j), u0, acc0);
-        if (second) acc1 = fmaf(load_as_float(wc, taps + j), u1, acc1);
+        if (wvec) {
+          acc0 = fmaf(wf[j & 3], u0, acc0);
+          acc1 = fmaf(wf[4 + (j & 3)], u1, acc1);
+        } else {
+          acc0 = fmaf(load_as_float(wc, j), u0, acc0);
+          if (second) acc1 = fmaf(load_as_float(wc, taps + j), u1, acc1);
+        }
       }
       if (G.act == 1) {
         acc0 = acc0 / (1.0f + expf(-acc0));
@@ -232,10 +240,13 @@ int b200_short_conv(const void* in, int64_t ld_in, const b200_conv_group* groups
   int pairs = (ld_in % 2 == 0) && (tail_cols % 2 == 0) && (tail_slot_stride % 2 == 0) && (reinterpret_cast<uintptr_t>(in) % (2 * esz) == 0) &&
               (reinterpret_cast<uintptr_t>(tail) % (2 * esz) == 0);
   int max_dim = 0;
+  bool w16 = true;
   for (int i = 0; i < n_groups; ++i) {
     pairs = pairs && groups[i].dim % 2 == 0 && groups[i].col0 % 2 == 0;
+    w16 = w16 && reinterpret_cast<uintptr_t>(groups[i].w) % 16 == 0;
     max_dim = groups[i].dim > max_dim ? groups[i].dim : max_dim;
   }
+  if (pairs && w16) pairs |= 2;   // even channels times four taps: every pair's taps start on a 16-byte boundary
   cudaStream_t st = (cudaStream_t)stream;
   const int4* sq = reinterpret_cast<const int4*>(seqs);
   B200_FLOAT_TYPES(dtype, T, {
