@@ -16,8 +16,7 @@ continuing at its own position) and returns logits for the requested rows only.
 """
 from __future__ import annotations
 
-import contextlib
-from typing import Any, Dict, Iterator, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn as nn
