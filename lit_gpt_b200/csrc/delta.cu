@@ -152,9 +152,11 @@ __global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A, int L)
       const float* kt = ks + t * DKP + sub;
       const float* qt = qs + t * DKP + sub;
       // with D = g S (decayed state):  u = beta (v - D^T k),  S = D + k u^T,  o = S^T q = D^T q + (k . q) u
-      // so the three dot products over the key axis are independent and share the rounds of one reduction
+      // so the three dot products over the key axis are independent and share the rounds of one reduction; with few numbers per
+      // lane each is summed in two interleaved halves (measured: 0.66 -> 0.57 us per token there, a loss with 16 per lane)
+      constexpr int NA = KPL <= 8 ? 2 : 1;
       float kr[kDrKPL];
-      float dk_ = 0.f, dq_ = 0.f, kq_ = 0.f;
+      float dk_[2] = {0.f, 0.f}, dq_[2] = {0.f, 0.f}, kq_[2] = {0.f, 0.f};
       if (CHANNEL) {
         const float* gt = gs + t * DKP + sub;
 #pragma unroll
@@ -162,9 +164,9 @@ __global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A, int L)
           kr[r] = kt[r * LPC];
           const float qv = qt[r * LPC];
           S[r] *= gt[r * LPC];
-          dk_ = fmaf(S[r], kr[r], dk_);
-          dq_ = fmaf(S[r], qv, dq_);
-          kq_ = fmaf(kr[r], qv, kq_);
+          dk_[r % NA] = fmaf(S[r], kr[r], dk_[r % NA]);
+          dq_[r % NA] = fmaf(S[r], qv, dq_[r % NA]);
+          kq_[r % NA] = fmaf(kr[r], qv, kq_[r % NA]);
         }
       } else {
         const float g = gs[t];
@@ -173,21 +175,22 @@ __global__ void __launch_bounds__(kDrThreads) delta_rule_kernel(DrArgs A, int L)
           kr[r] = kt[r * LPC];
           const float qv = qt[r * LPC];
           S[r] *= g;
-          dk_ = fmaf(S[r], kr[r], dk_);
-          dq_ = fmaf(S[r], qv, dq_);
-          kq_ = fmaf(kr[r], qv, kq_);
+          dk_[r % NA] = fmaf(S[r], kr[r], dk_[r % NA]);
+          dq_[r % NA] = fmaf(S[r], qv, dq_[r % NA]);
+          kq_[r % NA] = fmaf(kr[r], qv, kq_[r % NA]);
         }
       }
+      float dks = dk_[0] + dk_[1], dqs = dq_[0] + dq_[1], kqs = kq_[0] + kq_[1];
 #pragma unroll
       for (int o = LPC / 2; o > 0; o >>= 1) {
-        dk_ += __shfl_xor_sync(0xffffffffu, dk_, o);
-        dq_ += __shfl_xor_sync(0xffffffffu, dq_, o);
-        kq_ += __shfl_xor_sync(0xffffffffu, kq_, o);
+        dks += __shfl_xor_sync(0xffffffffu, dks, o);
+        dqs += __shfl_xor_sync(0xffffffffu, dqs, o);
+        kqs += __shfl_xor_sync(0xffffffffu, kqs, o);
       }
-      const float u = bs[t] * (vs[t * COLS + cl] - dk_);
+      const float u = bs[t] * (vs[t * COLS + cl] - dks);
 #pragma unroll
       for (int r = 0; r < kDrKPL; ++r) S[r] = fmaf(kr[r], u, S[r]);
-      if (sub == 0 && col_ok) A.out[(int64_t)(first + t0 + t) * A.ldo + (int64_t)h * dv + col] = fmaf(kq_, u, dq_);
+      if (sub == 0 && col_ok) A.out[(int64_t)(first + t0 + t) * A.ldo + (int64_t)h * dv + col] = fmaf(kqs, u, dqs);
     }
   }
   if (col_ok) {
