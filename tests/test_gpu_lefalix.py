@@ -78,6 +78,14 @@ CFG_WIDE = config(width=64, vocab=120, eps=1e-3, layers=[
     parallel_layer(window(3, 1, 24, 24, 4, size=33, rot_dims=24, base=1e4, scale=0.35), delta(4, 2, 16, 16, 3), moe(8, 4, 24, 4, 3)),
 ])
 
+# head sizes the tensor-core prompt kernel takes in bf16 (64 and 128, grouped), a window that ends inside a key tile, a key size
+# that spreads a state column over 32 lanes for prompts and 8 for single tokens, a repeated run that starts at the first layer
+CFG_TILES = config(width=96, vocab=140, loop=(0, 2, 2), layers=[
+    parallel_layer(window(4, 2, 64, 64, 3, size=40, rot_dims=32, base=1e5, scaling=(4.0, 64, 8.0, 1.0)), delta(2, 1, 64, 32, 3), moe(8, 2, 48, 4, 2)),
+    channel_layer(delta(2, 2, 128, 48, 4), dense(200)),
+    parallel_layer(window(2, 1, 128, 128, 2, size=100, rot_dims=64, base=1e4, scale=0.2), delta(2, 2, 48, 64, 4), dense(160)),
+])
+
 
 def checkpoint(cfg, seed, sharp=1.0):
     """Random bf16 weights of a size that keeps every mechanism alive; `sharp` multiplies the attention scale's effect by scaling
@@ -495,12 +503,12 @@ def test_sandwich_residual_and_activations(dtype, d):
 # ---------------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("cfg,seed", [(CFG_ODD, 11), (CFG_WIDE, 12)])
+@pytest.mark.parametrize("cfg,seed", [(CFG_ODD, 11), (CFG_WIDE, 12), (CFG_TILES, 13)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prompt_matches_oracle(cfg, seed, dtype):
     w = checkpoint(cfg, seed)
     model = build(cfg, w, dtype)
-    toks = tokens_for(cfg, 90, seed)
+    toks = tokens_for(cfg, 150 if cfg is CFG_TILES else 90, seed)
     got = model.step(toks, [(1, 0, len(toks))])
     assert got.dtype == torch.float32
     assert_close(got, O.forward(cfg, w, toks), dtype)
@@ -520,7 +528,7 @@ def test_layers_follow_the_oracle_one_by_one():
         assert rel_err(x, layers[i]) < 1e-5, f"residual stream after layer run {i}"
 
 
-@pytest.mark.parametrize("cfg", [CFG_ODD, CFG_WIDE])
+@pytest.mark.parametrize("cfg", [CFG_ODD, CFG_WIDE, CFG_TILES])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_decoding_token_by_token_equals_prefill(dtype, cfg):
     w = checkpoint(cfg, 31)
@@ -722,3 +730,33 @@ def test_trace_runner_end_to_end(tmp_path, dtype):
     if dtype == "bfloat16":
         got = torch.cat([torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, cfg["vocab"])) for step in want])
         assert_close(got, torch.cat(list(want.values())), torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prompts_on_the_tensor_cores_then_decoding_over_their_rings(dtype):
+    """Two unequal prompts in one step (bf16: the tensor-core tiles for both attention layers), each longer than one window and
+    shorter than the other, then 45 single-token steps that slide both windows over the prompt's ring rows, and a third request
+    that arrives in portions while the others decode."""
+    from lit_gpt_b200.generate.serve import Session
+
+    cfg = CFG_TILES
+    w = checkpoint(cfg, 61)
+    model = build(cfg, w, dtype)
+    session = Session(model, slots=2)
+    a, b, c = tokens_for(cfg, 115, 62), tokens_for(cfg, 95, 63), tokens_for(cfg, 60, 64)
+    want = {r: O.forward(cfg, w, t) for r, t in (("a", a), ("b", b), ("c", c))}
+    out = session.step([("a", a[:70], [0, 39, 40, 69]), ("b", b[:50], [49])])
+    assert_close(out, torch.cat([want["a"][[0, 39, 40, 69]], want["b"][49:50]]), dtype, "prompts")
+    got = {"a": [], "b": [], "c": []}
+    for i in range(45):
+        entries = [("a", [a[70 + i]], [0]), ("b", [b[50 + i]], [0])]
+        if i % 15 == 5:                       # c's portions of 20 tokens ride along with the single-token steps
+            j = (i // 15) * 20
+            entries.append(("c", c[j : j + 20], None))
+        out = session.step(entries)
+        got["a"].append(out[0:1]); got["b"].append(out[1:2])
+        if len(entries) == 3:
+            got["c"].append(out[2:])
+    assert_close(torch.cat(got["a"]), want["a"][70:115], dtype, "a")
+    assert_close(torch.cat(got["b"]), want["b"][50:95], dtype, "b")
+    assert_close(torch.cat(got["c"]), want["c"], dtype, "c")
