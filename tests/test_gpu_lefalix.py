@@ -352,12 +352,13 @@ def test_sink_takes_probability_once_and_unscaled():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("channel", [False, True])
-@pytest.mark.parametrize("cuts,dim", [([41], 12), ([1] * 41, 12), ([2, 2, 1, 20, 2, 3, 9, 2], 12), ([40, 1], 12), ([30, 1, 10], 40), ([3, 37, 1], 72)])
-def test_delta_rule_alone(dtype, channel, cuts, dim):
+@pytest.mark.parametrize("cuts,dim,taps", [([41], 12, 4), ([1] * 41, 12, 4), ([2, 2, 1, 20, 2, 3, 9, 2], 12, 4), ([40, 1], 12, 4), ([30, 1, 10], 40, 4),
+                                           ([3, 37, 1], 72, 4), ([2, 3, 1, 1, 30, 4], 12, 7), ([41], 12, 9)])
+def test_delta_rule_alone(dtype, channel, cuts, dim, taps):
     """Grouped heads, convolution tail with its activation, unit vectors, decay per head or per channel, write-then-read order,
     gated norm -- with the state carried over every cut (prompts and single tokens spread a state column over different numbers
     of lanes for the larger key sizes: both read the same stored state)."""
-    m = delta(4, 2, dim, 10, 4)
+    m = delta(4, 2, dim, 10, taps)      # more taps than the unrolled cases, and portions shorter than the taps
     layer = channel_layer(m, None) if channel else parallel_layer(window(1, 1, 4, 4, 1, size=2, rot_dims=4), m, None)
     cfg, w, model = _one_layer(layer, 24, dtype, seed=13)
     g = torch.Generator().manual_seed(15)
