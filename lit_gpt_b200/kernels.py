@@ -931,8 +931,8 @@ def window_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_ring: torch
                                     n_kv_head * dv, seqs.data_ptr(), row_seq.data_ptr(), q.shape[0], _code(q), st), "ring_store")
         return out
     # the any-size kernels store the step's rows into the rings themselves (single rows: inside the attention kernel)
-    args = C.WindowAttnArgs(row_seq=row_seq.data_ptr(), rows=q.shape[0], q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
-                            ldo=out.stride(0), k_ring=k_ring.data_ptr(), v_ring=v_ring.data_ptr(), sink=C.ptr(sink), seqs=seqs.data_ptr(),
+    args = C.WindowAttnArgs(row_seq=row_seq.data_ptr(), rows=q.shape[0], q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(),
+                            ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0), ldo=out.stride(0), k_ring=k_ring.data_ptr(), v_ring=v_ring.data_ptr(), sink=C.ptr(sink), seqs=seqs.data_ptr(),
                             n_seqs=seqs.shape[0], max_q_len=max_q_len, ring=ring, n_head=n_head, n_kv_head=n_kv_head, dk=dk, dv=dv, window=window,
                             scale=float(scale), dtype=_code(q))
     C.check(lib.b200_window_attn(ctypes.byref(args), st), "window_attn")

@@ -299,6 +299,6 @@ class Lefalix(SlotServed, nn.Module):
         if start + T > self.max_seq_length:
             raise ValueError(f"Cannot forward sequence of length {start + T}, max seq length is only {self.max_seq_length}.")
         seq_state = torch.tensor([(b * T, T, start, b) for b in range(B)], dtype=torch.int32).to(dev)
-        batch = RaggedBatch(row_pos=None, row_slot=None, cache_rows=None, decode=False, context_hint=start + T, max_q_len=T, seq_state=seq_state, identity_ctx=start == 0,
-                            row_seq=ar.repeat_interleave(T))
+        batch = RaggedBatch(row_pos=None, row_slot=None, cache_rows=None, decode=False, context_hint=start + T, max_q_len=T, seq_state=seq_state,
+                            identity_ctx=start == 0, row_seq=ar.repeat_interleave(T))
         return self._run(idx.reshape(B * T).to(torch.int32), batch, None).view(B, T, -1)
